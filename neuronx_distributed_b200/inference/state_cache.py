@@ -21,6 +21,7 @@ class StepContext:
     slots: torch.Tensor         # state slot of each row
     pos0: torch.Tensor          # position of each row's first token
     fresh: bool                 # the rows start their sequences in this step
+    scratch: Dict = dataclasses.field(default_factory=dict)   # what one layer leaves for a later layer of the same step
 
 
 class SequenceStateManager:

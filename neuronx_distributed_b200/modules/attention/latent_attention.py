@@ -13,7 +13,14 @@ per ring chunk scores all heads against the chunk's rows and weights the same ro
 bound by arithmetic, so they expand every head's keys and values once and spend ``dim + rot_dim + vdim`` multiply-adds per
 (query, key, head) instead of ``2 kv_rank + rot_dim``: in bfloat16 with sizes in whole 16s as ONE kernel that keeps scores and
 weights on chip (``csrc/seqmix/latent_prefill.cu``), otherwise (float, odd sizes) as block matrix products around a float softmax
-kernel.  With ``block_products=False`` both run the one-kernel absorbed form."""
+kernel.  With ``block_products=False`` both run the one-kernel absorbed form.
+
+Options: ``q_rank = 0`` — queries are one direct projection of the input (no query latent); ``head_gate`` — head h's output is
+multiplied by ``sigmoid(W_g h)_h``; ``kv_key`` with ``shares_kv`` — the layer has no key/value down-projection and no cache of its
+own: it attends over the latents and rotated key parts another layer (same ``kv_rank``, ``rot_dim`` and rotation) prepared in this
+step (``ctx.scratch[kv_key]``) and keeps in ITS ring (passed in as ``st``), with its own ``W_uk``, ``W_uv``, queries and window; the
+owning layer is built with ``kv_key`` and ``ring_window`` = the widest window among its users.  Rotation pairs are rotate-half; a
+checkpoint with interleaved pairs is de-interleaved when it is loaded (``utils.deinterleave_rows``)."""
 from __future__ import annotations
 
 from typing import Dict, Tuple
@@ -28,33 +35,57 @@ from ...ops import seqmix
 class LatentWindowAttention(nn.Module):
     def __init__(self, width: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, q_rank: int, window: int,
                  scale: float, rot_base: float, rot_dims: int, eps: float, dtype: torch.dtype = torch.bfloat16, device=None,
-                 max_seq_len: int = 1 << 30, block_products: bool = True, query_block: int = 128):
+                 max_seq_len: int = 1 << 30, block_products: bool = True, query_block: int = 128, head_gate: bool = False,
+                 kv_key=None, shares_kv: bool = False, ring_window: int = 0):
         super().__init__()
+        assert not shares_kv or kv_key is not None, "a layer that borrows keys names their owner"
         self.heads, self.dim, self.rot_dim, self.vdim, self.kv_rank, self.q_rank = heads, dim, rot_dim, vdim, kv_rank, q_rank
         self.window, self.scale, self.rot_dims, self.eps, self.dtype = window, scale, rot_dims, eps, dtype
-        self.ring = max(1, min(window, max_seq_len))
+        self.ring = max(1, min(max(window, ring_window), max_seq_len))
+        self.kv_key, self.shares_kv = kv_key, shares_kv
         self.block_products, self.query_block = block_products, query_block
         self.fused_prompt = True          # bfloat16 prompts of fitting sizes in one kernel (csrc/seqmix/latent_prefill.cu)
         self.max_seq_len = max_seq_len
         mk = lambda *s: nn.Parameter(torch.zeros(*s, dtype=dtype, device=device), requires_grad=False)
         f32 = lambda *s: nn.Parameter(torch.ones(*s, dtype=torch.float32, device=device), requires_grad=False)
-        self.dq, self.dq_norm, self.uq = mk(q_rank, width), f32(q_rank), mk(heads * (dim + rot_dim), q_rank)
-        self.dkv, self.dkv_norm = mk(kv_rank + rot_dim, width), f32(kv_rank)
+        if q_rank:
+            self.dq, self.dq_norm, self.uq = mk(q_rank, width), f32(q_rank), mk(heads * (dim + rot_dim), q_rank)
+        else:
+            self.q_proj = mk(heads * (dim + rot_dim), width)
+        if not shares_kv:
+            self.dkv, self.dkv_norm = mk(kv_rank + rot_dim, width), f32(kv_rank)
+        self.head_gate = mk(heads, width) if head_gate else None
         self.uk, self.uv = mk(heads, dim, kv_rank), mk(heads, vdim, kv_rank)          # per head [out, in]
         self.o = mk(width, heads * vdim)
         self.register_buffer("inv_freq", seqmix.rotary_inv_freq(rot_dims, rot_base, device), persistent=False)
 
     def state_spec(self) -> Dict[str, Tuple[Tuple[int, ...], torch.dtype]]:
+        if self.shares_kv:
+            return {}
         return {"kv": ((self.ring, self.kv_rank + self.rot_dim), self.dtype)}
+
+    def _gated(self, heads: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+        """``heads [N, H*vdim]`` times the per-head sigmoid gates read from the layer's input (float logits)."""
+        if self.head_gate is None:
+            return heads
+        return seqmix.sigmoid_gate_mul_(heads, seqmix.linear_f32(h.view(heads.shape[0], -1), self.head_gate))
 
     def forward(self, h: torch.Tensor, ctx, st: Dict[str, torch.Tensor]) -> torch.Tensor:
         B, S, _ = h.shape
         N, H, D, R = B * S, self.heads, self.dim, self.rot_dim
-        cq = seqmix.rms_norm(F.linear(h.view(N, -1), self.dq), self.dq_norm, self.eps)
-        q = F.linear(cq, self.uq).view(B, S, H, D + R)
-        kv = F.linear(h, self.dkv)
-        rows = seqmix.latent_kv_store(kv, self.dkv_norm, self.eps, self.inv_freq, self.rot_dims, ctx.pos0, ctx.lens, ctx.slots, st["kv"],
-                                      want_rows=ctx.fresh)
+        if self.q_rank:
+            cq = seqmix.rms_norm(F.linear(h.view(N, -1), self.dq), self.dq_norm, self.eps)
+            q = F.linear(cq, self.uq).view(B, S, H, D + R)
+        else:
+            q = F.linear(h, self.q_proj).view(B, S, H, D + R)
+        if self.shares_kv:
+            rows = ctx.scratch[self.kv_key] if ctx.fresh else None
+        else:
+            kv = F.linear(h, self.dkv)
+            rows = seqmix.latent_kv_store(kv, self.dkv_norm, self.eps, self.inv_freq, self.rot_dims, ctx.pos0, ctx.lens, ctx.slots, st["kv"],
+                                          want_rows=ctx.fresh)
+            if self.kv_key is not None and ctx.fresh:
+                ctx.scratch[self.kv_key] = rows
         seqmix.rope_q_(q, D, self.rot_dims, self.inv_freq, ctx.pos0)
         if ctx.fresh and self.block_products:
             if self.fused_prompt and seqmix.latent_prompt_fused_ok(q, D, R, self.kv_rank + R, self.vdim):
@@ -63,7 +94,7 @@ class LatentWindowAttention(nn.Module):
                 heads = seqmix.latent_prompt_attention(q, kx, rows, vx, ctx.lens, D, R, self.vdim, self.window, self.scale)
             else:
                 heads = self._attend_prompt(q, rows, ctx)
-            return F.linear(heads, self.o).view(B, S, -1)
+            return F.linear(self._gated(heads, h), self.o).view(B, S, -1)
         qa = torch.bmm(q.view(N, H, D + R)[:, :, :D].transpose(0, 1), self.uk)                       # [H,N,D] @ [H,D,C]
         if S == 1 and not ctx.fresh and self.kv_rank + R <= seqmix.LATENT_ROW_MAX:
             o = seqmix.latent_window_attention(qa, q, D, st["kv"], ctx.slots, ctx.pos0, ctx.lens, self.window, self.scale)
@@ -74,7 +105,7 @@ class LatentWindowAttention(nn.Module):
         else:
             o = seqmix.latent_window_attention(qa, q, D, st["kv"], ctx.slots, ctx.pos0, ctx.lens, self.window, self.scale)
         ov = torch.bmm(o, self.uv.transpose(1, 2))                                                     # [H,N,C] @ [H,C,V]
-        return F.linear(ov.transpose(0, 1).reshape(N, H * self.vdim), self.o).view(B, S, -1)
+        return F.linear(self._gated(ov.transpose(0, 1).reshape(N, H * self.vdim), h), self.o).view(B, S, -1)
 
     def _attend_prompt(self, q: torch.Tensor, rows: torch.Tensor, ctx) -> torch.Tensor:
         """A prompt in the expanded form: every head's keys ``[W_uk c | rotated part]`` and values ``W_uv c`` are formed by two

@@ -55,3 +55,18 @@ def apply_rotary_polar_compatible(query: torch.Tensor, key: torch.Tensor, freqs_
         return o.flatten(-2).to(x.dtype)
 
     return rot(xq), rot(xk)
+
+
+def deinterleave_index(heads: int, head_dim: int, off: int, dims: int) -> torch.Tensor:
+    """Row order that turns interleaved rotation pairs into rotate-half pairs: inside every head of ``head_dim`` rows, the ``dims``
+    rows from ``off`` on are reordered ``0, 2, 4, ..., 1, 3, 5, ...`` (pair i = rows ``2i, 2i+1`` becomes rows ``i, i + dims/2``); the
+    other rows stay.  Reordering the rows of BOTH projections of a dot product (queries and keys) the same way leaves every score
+    unchanged, so a checkpoint whose rotation pairs neighbours can be served by kernels that pair the two halves."""
+    inner = torch.arange(head_dim)
+    inner[off:off + dims] = off + torch.cat([torch.arange(0, dims, 2), torch.arange(1, dims, 2)])
+    return (torch.arange(heads)[:, None] * head_dim + inner[None, :]).reshape(-1)
+
+
+def deinterleave_rows(w: torch.Tensor, heads: int, head_dim: int, off: int, dims: int) -> torch.Tensor:
+    """``w [heads * head_dim, ...]`` with its rows reordered by :func:`deinterleave_index`."""
+    return w[deinterleave_index(heads, head_dim, off, dims).to(w.device)]

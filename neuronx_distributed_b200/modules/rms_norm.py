@@ -109,3 +109,26 @@ class OffsetRMSNorm(nn.Module):
 
         seqmix.add_rms_norm_(res.view(-1, res.shape[-1]), y.reshape(-1, y.shape[-1]), self.weight, self.eps)
         return res
+
+
+class GainOnlyLayerNorm(nn.Module):
+    """Layer norm with a gain and no bias: ``(x - mean) / sqrt(mean((x - mean)^2) + eps) * w``, statistics in float.  ``forward``
+    gives the sublayer's input in ``out_dtype``; ``add_to(res, y)`` is the closing norm of a sandwich block, ``res += norm(y)`` with
+    ``res`` a float stream (one kernel each: the RMS-norm kernels of ``csrc/seqmix/norms.cu`` with the mean taken off first)."""
+
+    def __init__(self, width: int, eps: float = 1e-6, device=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(width, dtype=torch.float32, device=device), requires_grad=False)
+        self.eps = eps
+
+    def forward(self, input: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        from ..ops import seqmix
+
+        x = input
+        return seqmix.rms_norm(x.reshape(-1, x.shape[-1]), self.weight, self.eps, None, out_dtype or x.dtype, center=True).view(x.shape)
+
+    def add_to(self, res: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        from ..ops import seqmix
+
+        seqmix.add_rms_norm_(res.view(-1, res.shape[-1]), y.reshape(-1, y.shape[-1]), self.weight, self.eps, center=True)
+        return res

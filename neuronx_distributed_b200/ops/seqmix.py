@@ -30,11 +30,13 @@ CSRC = _ext.PKG_DIR.parent / "csrc" / "seqmix"
 GROUPS = {
     "core": (["short_conv.cu", "norms.cu", "activations.cu", "embed.cu", "bind_core.cpp"],
              ["short_conv", "rms_norm", "add_rms_norm_", "xielu", "gelu_erf", "silu_mul", "indexed_gemv", "moe_combine", "embed_sinusoid",
-              "group_rms_norm_gated", "route_topk", "small_linear_f32"]),
+              "group_rms_norm_gated", "route_topk", "small_linear_f32", "clamped_glu", "sigmoid_gate_mul_", "rotary_qkv_f32"]),
     "latent": (["latent_attention.cu", "latent_decode.cu", "latent_prefill.cu", "bind_latent.cpp"],
                ["latent_kv_store", "rope_q_", "latent_window_attention", "window_softmax", "latent_prompt_attention",
                 "latent_prompt_attention_fits"]),
-    "linrec": (["linear_recurrence.cu", "gla_chunked.cu", "bind_linrec.cpp"], ["gla_scan", "rglru_scan"]),
+    "linrec": (["linear_recurrence.cu", "gla_chunked.cu", "bind_linrec.cpp"], ["gla_scan", "rglru_scan", "retention_scan"]),
+    "headmix": (["headmix_attention.cu", "headmix_prefill.cu", "bind_headmix.cpp"],
+                ["headmix_qk_prepare", "headmix_attention_prompt", "headmix_attention_token"]),
     "window": (["window_attention.cu", "window_prefill.cu", "bind_window.cpp"], ["window_qk_prepare", "window_attention_prompt", "window_attention_token"]),
     "matrec": (["matrix_recurrence.cu", "bind_matrec.cpp"], ["gated_delta_scan", "ssd_scan"]),
 }
@@ -142,26 +144,32 @@ def short_conv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], s
 
 # --------------------------------------------------------------------------------------------------------------------------- norms
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float, gate: Optional[torch.Tensor] = None,
-             out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """Rows of ``x [rows, C]`` divided by their root mean square, times ``w`` (``[C]`` or one number), times ``silu(gate)``."""
+             out_dtype: Optional[torch.dtype] = None, center: bool = False) -> torch.Tensor:
+    """Rows of ``x [rows, C]`` divided by their root mean square, times ``w`` (``[C]`` or one number), times ``silu(gate)``.
+    ``center``: the row's mean is taken off first (a layer norm with a gain and no bias: the statistics are the mean and the mean
+    squared deviation)."""
     out_dtype = out_dtype or x.dtype
     if _cuda(x):
         _ext.count_launch()
-        return ext().rms_norm(x, w, eps, gate, out_dtype == torch.bfloat16)
+        return ext().rms_norm(x, w, eps, gate, out_dtype == torch.bfloat16, center)
     xf = x.float()
+    if center:
+        xf = xf - xf.mean(-1, keepdim=True)
     y = xf / torch.sqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w
     if gate is not None:
         y = y * F.silu(gate.float())
     return y.to(out_dtype)
 
 
-def add_rms_norm_(res: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
-    """``res`` (float ``[rows, C]``) ``+= y / rms(y) * w`` in place."""
+def add_rms_norm_(res: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, center: bool = False) -> torch.Tensor:
+    """``res`` (float ``[rows, C]``) ``+= y / rms(y) * w`` in place (``center``: y's mean is taken off first)."""
     if _cuda(y):
         _ext.count_launch()
-        ext().add_rms_norm_(res, y, w, eps)
+        ext().add_rms_norm_(res, y, w, eps, center)
         return res
     yf = y.float()
+    if center:
+        yf = yf - yf.mean(-1, keepdim=True)
     res += yf / torch.sqrt(yf.pow(2).mean(-1, keepdim=True) + eps) * w
     return res
 
@@ -459,8 +467,10 @@ def embed_sinusoid(tokens: torch.Tensor, table: torch.Tensor, scale: float, inv_
 
 # ------------------------------------------------------------------------------------------------------------- grouped gated norm
 def group_rms_norm_gated(x: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, groups: int, eps: float, gate_first: bool,
-                         out: Optional[torch.Tensor] = None, out_scale: float = 1.0, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """Rows of ``x [rows, C]`` in ``groups`` equal parts, each divided by its own root mean square, with a ``silu(gate)`` factor:
+                         out: Optional[torch.Tensor] = None, out_scale: float = 1.0, out_dtype: Optional[torch.dtype] = None,
+                         gate_act: str = "silu") -> torch.Tensor:
+    """Rows of ``x [rows, C]`` in ``groups`` equal parts, each divided by its own root mean square, with a ``silu(gate)`` factor
+    (``gate_act="sigmoid"``: a ``sigmoid(gate)`` factor):
     ``gate_first``: ``rms_g(x * silu(gate)) * w`` (the gate enters the statistics); otherwise ``rms_g(x) * w * silu(gate)``.
     ``w`` holds ``C`` numbers or ``C / groups`` (shared by the groups).  The result times ``out_scale`` goes to ``out`` (any row
     stride) or a new ``[rows, C]`` tensor of ``out_dtype``."""
@@ -469,9 +479,9 @@ def group_rms_norm_gated(x: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, g
         out = torch.empty(rows, C, dtype=out_dtype or gate.dtype, device=x.device)
     if _cuda(x):
         _ext.count_launch()
-        ext().group_rms_norm_gated(x, gate, w, groups, eps, gate_first, out, out_scale)
+        ext().group_rms_norm_gated(x, gate, w, groups, eps, gate_first, out, out_scale, gate_act == "sigmoid")
         return out
-    xf, g = x.float(), F.silu(gate.float())
+    xf, g = x.float(), (torch.sigmoid(gate.float()) if gate_act == "sigmoid" else F.silu(gate.float()))
     if gate_first:
         xf = xf * g
     xg = xf.view(rows, groups, C // groups)
@@ -570,7 +580,8 @@ def gated_delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, braw: to
     """Gated delta rule.  ``q, k [B,S,G,D]``, ``v [B,S,H,V]`` (views), ``braw, araw [B,S,H]`` float pre-activations → float
     ``[B,S,H,V]``.  Head h reads q/k head ``h // (H/G)``; q and k are made unit vectors (``x / sqrt(sum x^2 + 1e-6)``), q also
     times ``D^-1/2``; ``beta = sigmoid(braw)``, ``g = exp(-exp(a_log) softplus(araw + dt_bias))``; per token
-    ``M <- g M; u = beta (v - M^T k); M <- M + k u^T; o = M^T q``.  ``state [slots,H,D,V]`` float."""
+    ``M <- g M; u = beta (v - M^T k); M <- M + k u^T; o = M^T q``.  ``state [slots,H,D,V]`` float.  With ``araw [B,S,H,D]`` and
+    ``dt_bias [H*D]`` the decay is one number per head AND key channel, ``g [H,D]``, which scales the rows of M."""
     if _cuda(q):
         _ext.count_launch()
         return ext().gated_delta_scan(q, k, v, braw, araw, a_log, dt_bias, state, _i32(slots), _i32(lens), fresh)
@@ -580,12 +591,15 @@ def gated_delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, braw: to
     qf = (qf / torch.sqrt(qf.pow(2).sum(-1, keepdim=True) + 1e-6) * D ** -0.5).repeat_interleave(H // G, 2)
     kf = (kf / torch.sqrt(kf.pow(2).sum(-1, keepdim=True) + 1e-6)).repeat_interleave(H // G, 2)
     vf, beta = v.float(), torch.sigmoid(braw.float())
-    g = torch.exp(-torch.exp(a_log) * F.softplus(araw.float() + dt_bias))
+    if araw.dim() == 4:
+        g = torch.exp(-torch.exp(a_log)[:, None] * F.softplus(araw.float() + dt_bias.view(H, D)))[..., None]      # [B,S,H,D,1]
+    else:
+        g = torch.exp(-torch.exp(a_log) * F.softplus(araw.float() + dt_bias))[..., None, None]                    # [B,S,H,1,1]
     st = torch.zeros(B, H, D, V) if fresh else state[slots.long()].clone()
     out = torch.zeros(B, S, H, V)
     for t in range(S):
         live = (t < lens)[:, None, None, None]
-        M = g[:, t, :, None, None] * st
+        M = g[:, t] * st
         u = beta[:, t, :, None] * (vf[:, t] - torch.einsum("bhdv,bhd->bhv", M, kf[:, t]))
         M = M + kf[:, t, :, :, None] * u[:, :, None, :]
         st = torch.where(live, M, st)
@@ -617,6 +631,171 @@ def ssd_scan(x: torch.Tensor, bm: torch.Tensor, cm: torch.Tensor, dtraw: torch.T
         y = torch.einsum("bhnv,bhn->bhv", st, cf[:, t]) + dskip[None, :, None] * xf[:, t]
         out[:, t] = torch.where(live[..., 0], y, out[:, t])
     state[slots.long()] = st
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ gated feed-forward, output gates
+def clamped_glu(gu: torch.Tensor, limit: float, slope: float) -> torch.Tensor:
+    """``gu [M, 2F]`` (gate columns, then up columns) → ``[M, F]``: ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``,
+    ``g * sigmoid(slope * g) * (u + 1)``."""
+    if _cuda(gu):
+        _ext.count_launch()
+        return ext().clamped_glu(gu, float(limit), float(slope))
+    half = gu.shape[1] // 2
+    g, u = gu[:, :half].float().clamp(max=limit), gu[:, half:].float().clamp(-limit, limit)
+    return (g * torch.sigmoid(slope * g) * (u + 1.0)).to(gu.dtype)
+
+
+def sigmoid_gate_mul_(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """``x [N, C]`` (contiguous) times ``sigmoid(gate [N, Cg])`` in place, each gate number covering ``C / Cg`` consecutive
+    coordinates of its row (``Cg = C``: one gate per coordinate; ``Cg = heads``: one per head).  ``gate``'s row stride is free."""
+    if _cuda(x):
+        _ext.count_launch()
+        ext().sigmoid_gate_mul_(x, gate)
+        return x
+    N, C = x.shape
+    rep = C // gate.shape[1]
+    x.copy_((x.float().view(N, -1, rep) * torch.sigmoid(gate.float())[..., None]).view(N, C).to(x.dtype))
+    return x
+
+
+# ------------------------------------------------------------------------------------------------------- retention (fixed decay)
+def rotary_qkv_f32(p: torch.Tensor, hq: int, hk: int, D: int, dims: int, inv_freq: torch.Tensor, pos0: torch.Tensor, q_scale: float,
+                   k_scale: float) -> torch.Tensor:
+    """``p [B,S,C]`` (a stacked projection: ``hq`` query heads of D numbers, ``hk`` key heads of D numbers, then anything) → float
+    ``[B,S,C]``: the first ``dims`` coordinates of every query and key head rotated (rotate-half pairs) at positions
+    ``pos0[b] + t`` in float, queries times ``q_scale``, keys times ``k_scale``, the rest copied."""
+    if _cuda(p):
+        _ext.count_launch()
+        return ext().rotary_qkv_f32(p, hq, hk, D, dims, inv_freq, _i32(pos0), float(q_scale), float(k_scale))
+    B, S, C = p.shape
+    f = p.float()
+    pos = (pos0.long()[:, None] + torch.arange(S)[None, :])[:, :, None]
+    q = _rotate(f[..., :hq * D].reshape(B, S, hq, D), pos, inv_freq, dims) * q_scale
+    k = _rotate(f[..., hq * D:(hq + hk) * D].reshape(B, S, hk, D), pos, inv_freq, dims) * k_scale
+    return torch.cat([q.reshape(B, S, -1), k.reshape(B, S, -1), f[..., (hq + hk) * D:]], -1)
+
+
+def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, slots: torch.Tensor,
+                   lens: torch.Tensor, fresh: bool) -> torch.Tensor:
+    """Linear attention with ONE fixed decay per head: float ``q, k [B,S,H,D]``, ``v [B,S,H,V]`` (views), ``decay [H]`` float → float
+    ``[B,S,H,V]``: ``S_t = decay_h S_(t-1) + k_t v_t^T``, ``o_t = S_t^T q_t`` (no softmax, no denominator; scales are the
+    caller's).  ``state [slots,H,D,V]`` float is read (unless ``fresh``) and left at each row's last real token."""
+    if _cuda(q):
+        _ext.count_launch()
+        return ext().retention_scan(q, k, v, decay, state, _i32(slots), _i32(lens), fresh)
+    B, S, H, D = q.shape
+    V = v.shape[-1]
+    qf, kf, vf = q.float(), k.float(), v.float()
+    st = torch.zeros(B, H, D, V) if fresh else state[slots.long()].clone()
+    out = torch.zeros(B, S, H, V)
+    for t in range(S):
+        live = (t < lens)[:, None, None, None]
+        st = torch.where(live, decay[None, :, None, None] * st + kf[:, t, :, :, None] * vf[:, t, :, None, :], st)
+        out[:, t] = torch.where(live[..., 0], torch.einsum("bhdv,bhd->bhv", st, qf[:, t]), out[:, t])
+    state[slots.long()] = st
+    return out
+
+
+# -------------------------------------------------------------- softmax attention with scores mixed across heads and a sink term
+def headmix_qk_prepare(q: torch.Tensor, k: torch.Tensor, dims: int, inv_freq: torch.Tensor, pos0: torch.Tensor, lens: torch.Tensor,
+                       slots: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, want_rows: bool) -> Optional[torch.Tensor]:
+    """Queries and keys that double as values: ``q [B,S,H,D]``, ``k [B,S,G,D]`` (views; last dim contiguous).  The first ``dims``
+    coordinates of every query head are rotated IN PLACE (rotate-half pairs, in float, at positions ``pos0[b] + t``).  The keys as
+    they come are the VALUES; rotated the same way they are the KEYS.  The last ``ring`` real tokens of each row go to ``kcache``
+    (rotated) and ``vcache`` (as they come), both ``[slots, ring, G, D]``, at row ``position mod ring``; with ``want_rows`` the
+    rotated keys come back as ``[B,S,G,D]``."""
+    if _cuda(k):
+        _ext.count_launch()
+        rows = ext().headmix_qk_prepare(q, k, dims, inv_freq, _i32(pos0), _i32(lens), _i32(slots), kcache, vcache, want_rows)
+        return rows if want_rows else None
+    B, S = k.shape[:2]
+    pos = pos0.long()[:, None] + torch.arange(S)[None, :]
+    q.copy_(_rotate(q.float(), pos[:, :, None], inv_freq, dims).to(q.dtype))
+    rows = _rotate(k.float(), pos[:, :, None], inv_freq, dims).to(k.dtype)
+    ring = kcache.shape[1]
+    for b in range(B):
+        n = int(lens[b])
+        for t in range(max(0, n - ring), n):
+            kcache[int(slots[b]), int(pos[b, t]) % ring] = rows[b, t]
+            vcache[int(slots[b]), int(pos[b, t]) % ring] = k[b, t]
+    return rows if want_rows else None
+
+
+def _visible(i: torch.Tensor, j: torch.Tensor, chunk: int, window: int) -> torch.Tensor:
+    ok = (j <= i) & (j >= 0)
+    if chunk > 0:
+        ok = ok & (torch.div(i, chunk, rounding_mode="floor") == torch.div(j, chunk, rounding_mode="floor"))
+    if window > 0:
+        ok = ok & (i - j < window)
+    return ok
+
+
+def _headmix_softmax(raw: torch.Tensor, talk: Optional[torch.Tensor], sink: Optional[torch.Tensor], ok: torch.Tensor) -> torch.Tensor:
+    """``raw [B,H,Q,K]`` scaled scores, ``ok [B,1|H,Q,K]`` → weights: heads mixed by ``talk [H,H]``, softmax over the visible keys
+    whose denominator also holds ``exp(sink_h)``."""
+    sc = raw if talk is None else torch.einsum("hg,bgqk->bhqk", talk, raw)
+    sc = sc.masked_fill(~ok, float("-inf"))
+    if sink is not None:
+        sc = torch.cat([sc, sink.view(1, -1, 1, 1).expand(sc.shape[0], -1, sc.shape[2], 1)], -1)
+    p = torch.nan_to_num(torch.softmax(sc, -1), nan=0.0)
+    return p[..., :-1] if sink is not None else p
+
+
+def headmix_attention_prompt(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, coef: torch.Tensor, talk: Optional[torch.Tensor],
+                             sink: Optional[torch.Tensor], gate: Optional[torch.Tensor], lens: torch.Tensor, chunk: int, window: int,
+                             out: torch.Tensor) -> torch.Tensor:
+    """Prompts that start at position 0: ``q [B,S,H,D]``, ``k [B,S,G,D]``, ``v [B,S,G,V]`` (views); query head h uses key/value head
+    ``h // (H/G)``.  Score of head g: ``q_g . k * coef[g]`` (float); the heads' scores of a (query, key) pair are then mixed,
+    ``score_h = sum_g talk[h,g] score_g``.  Query i sees ``j <= i`` of its own aligned chunk of ``chunk`` positions (0: no chunks) and
+    within ``window`` positions back (0: no window).  Softmax in float with ``exp(sink[h])`` added to the denominator (no key, no
+    value).  The heads' results times ``sigmoid(gate [B,S,H*V])`` go to ``out [B*S, H*V]`` (row stride free); padded rows give
+    zeros."""
+    if _cuda(q):
+        _ext.count_launch()
+        ext().headmix_attention_prompt(q, k, v, coef, talk, sink, gate, _i32(lens), chunk, window, out)
+        return out
+    B, S, H, D = q.shape
+    G, V = k.shape[2], v.shape[3]
+    kk, vv = k.float().repeat_interleave(H // G, 2), v.float().repeat_interleave(H // G, 2)
+    raw = torch.einsum("bihd,bjhd->bhij", q.float(), kk) * coef.view(1, H, 1, 1)
+    i, j = torch.arange(S)[:, None], torch.arange(S)[None, :]
+    p = _headmix_softmax(raw, talk, sink, _visible(i, j, chunk, window)[None, None])
+    o = torch.einsum("bhij,bjhv->bihv", p, vv).reshape(B, S, H * V)
+    if gate is not None:
+        o = o * torch.sigmoid(gate.float())
+    o = torch.where((torch.arange(S)[None, :] < lens[:, None])[..., None], o, torch.zeros_like(o))
+    out[:, :H * V] = o.reshape(B * S, H * V).to(out.dtype)
+    return out
+
+
+def headmix_attention_token(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, coef: torch.Tensor, talk: Optional[torch.Tensor],
+                            sink: Optional[torch.Tensor], gate: Optional[torch.Tensor], slots: torch.Tensor, pos0: torch.Tensor,
+                            lens: torch.Tensor, chunk: int, window: int, out: torch.Tensor) -> torch.Tensor:
+    """Single tokens ``q [B,1,H,D]`` at positions ``pos0`` against their slots' rings (``kcache [slots, ring, G, D]``, ``vcache
+    [slots, ring, G, V]``; row ``j mod ring`` holds position j, the token's own row included; the ring is at least as long as the
+    longest visible stretch).  Scores, mixing, sink, gate and output layout as :func:`headmix_attention_prompt`; rows with ``lens == 0``
+    give zeros."""
+    if _cuda(q):
+        _ext.count_launch()
+        ext().headmix_attention_token(q, kcache, vcache, coef, talk, sink, gate, _i32(slots), _i32(pos0), _i32(lens), chunk, window, out)
+        return out
+    B, _, H, D = q.shape
+    ring, G, V = kcache.shape[1], kcache.shape[2], vcache.shape[3]
+    kb = kcache[slots.long()].float().repeat_interleave(H // G, 2)                                  # [B, ring, H, D]
+    vb = vcache[slots.long()].float().repeat_interleave(H // G, 2)
+    raw = torch.einsum("bhd,brhd->bhr", q[:, 0].float(), kb) * coef.view(1, H, 1)
+    p_ = pos0.long()[:, None]
+    back = torch.remainder(p_ - torch.arange(ring)[None, :], ring)                                   # distance back of ring row r
+    ok = _visible(p_, p_ - back, chunk, window)                                                      # [B, ring]
+    raw = torch.where(ok[:, None, :], raw, torch.zeros_like(raw))                                   # rows never written hold anything
+    vb = torch.where(ok[:, :, None, None], vb, torch.zeros_like(vb))
+    w = _headmix_softmax(raw[:, :, None, :], talk, sink, ok[:, None, None, :])[:, :, 0]             # [B,H,ring]
+    o = torch.einsum("bhr,brhv->bhv", w, vb).reshape(B, H * V)
+    if gate is not None:
+        o = o * torch.sigmoid(gate.float()).view(B, H * V)
+    o = torch.where((lens > 0)[:, None], o, torch.zeros_like(o))
+    out[:, :H * V] = o.to(out.dtype)
     return out
 
 
