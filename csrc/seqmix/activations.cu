@@ -2,6 +2,8 @@
 //   xielu        : z > 0: ap z^2 + z/2;  z <= 0: an (exp(z) - 1 - z) + z/2   (ap, an are positive numbers prepared by the caller)
 //   gelu_erf     : 0.5 z (1 + erf(z / sqrt 2))
 //   silu_mul     : silu(gate) * up for rows [gate | up]
+//   clamped_glu  : g = min(gate, limit), u = clamp(up, -limit, limit), g sigmoid(slope g) (u + 1) for rows [gate | up]
+//   sigmoid_gate_mul : x *= sigmoid(gate), one gate number per `rep` consecutive coordinates (a head, or one coordinate)
 //   indexed_gemv : out[m,:] = act(W[sel[m]] x[m,:]) for a few rows m, each with its own matrix out of a stack [E, O, I]
 //                  (token generation: the chosen experts' matrices are streamed once, a warp per output row); act 0: none,
 //                  1: gelu_erf, 2: the matrix stacks gate rows over up rows and out = silu(gate row . x) * (up row . x), O/2 columns;
@@ -242,6 +244,60 @@ void silu_mul(const void* gu, void* out, int bf, long rows, int F, cudaStream_t 
     const unsigned blocks = (unsigned)((rows * F + 255) / 256);
     if (bf) silu_mul_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)gu, rows, F, (bf16*)out);
     else silu_mul_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, rows, F, (float*)out);
+}
+
+__device__ __forceinline__ float clamped_glu_f(float g, float u, float limit, float slope) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * sigmoidf_(slope * g) * (u + 1.f);
+}
+
+template <typename T, bool VEC>
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, long rows, int F, float limit, float slope, T* __restrict__ out) {
+    const long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * (VEC ? 4 : 1);
+    if (i >= rows * F) return;
+    const long r = i / F;
+    const int c = (int)(i - r * F);
+    if (VEC) {
+        const float4 g = ld4(gu + r * 2 * F + c), u = ld4(gu + r * 2 * F + F + c);
+        st4(out + i, make_float4(clamped_glu_f(g.x, u.x, limit, slope), clamped_glu_f(g.y, u.y, limit, slope),
+                                 clamped_glu_f(g.z, u.z, limit, slope), clamped_glu_f(g.w, u.w, limit, slope)));
+    } else {
+        stf(out + i, clamped_glu_f(ldf(gu + r * 2 * F + c), ldf(gu + r * 2 * F + F + c), limit, slope));
+    }
+}
+
+void clamped_glu(const void* gu, void* out, int bf, long rows, int F, float limit, float slope, cudaStream_t s) {
+    if (rows * F == 0) return;
+    const size_t a4 = bf ? 8 : 16;
+    if (F % 4 == 0 && (uintptr_t)gu % a4 == 0 && (uintptr_t)out % a4 == 0) {
+        const unsigned vblocks = (unsigned)((rows * F / 4 + 255) / 256);
+        if (bf) clamped_glu_kernel<bf16, true><<<vblocks, 256, 0, s>>>((const bf16*)gu, rows, F, limit, slope, (bf16*)out);
+        else clamped_glu_kernel<float, true><<<vblocks, 256, 0, s>>>((const float*)gu, rows, F, limit, slope, (float*)out);
+        return;
+    }
+    const unsigned blocks = (unsigned)((rows * F + 255) / 256);
+    if (bf) clamped_glu_kernel<bf16, false><<<blocks, 256, 0, s>>>((const bf16*)gu, rows, F, limit, slope, (bf16*)out);
+    else clamped_glu_kernel<float, false><<<blocks, 256, 0, s>>>((const float*)gu, rows, F, limit, slope, (float*)out);
+}
+
+// x [rows, C] contiguous, gate [rows, C / rep] with its own row stride
+template <typename T, typename TG>
+__global__ void sigmoid_gate_mul_kernel(T* __restrict__ x, const TG* __restrict__ gate, long gate_stride, long rows, int C, int rep) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * C) return;
+    const long r = i / C;
+    const int c = (int)(i - r * C);
+    stf(x + i, ldf(x + i) * sigmoidf_(ldf(gate + r * gate_stride + c / rep)));
+}
+
+void sigmoid_gate_mul(void* x, int bf, const void* gate, int gate_bf, long gate_stride, long rows, int C, int rep, cudaStream_t s) {
+    if (rows * C == 0) return;
+    const unsigned blocks = (unsigned)((rows * C + 255) / 256);
+    if (bf && gate_bf) sigmoid_gate_mul_kernel<bf16, bf16><<<blocks, 256, 0, s>>>((bf16*)x, (const bf16*)gate, gate_stride, rows, C, rep);
+    else if (bf) sigmoid_gate_mul_kernel<bf16, float><<<blocks, 256, 0, s>>>((bf16*)x, (const float*)gate, gate_stride, rows, C, rep);
+    else if (gate_bf) sigmoid_gate_mul_kernel<float, bf16><<<blocks, 256, 0, s>>>((float*)x, (const bf16*)gate, gate_stride, rows, C, rep);
+    else sigmoid_gate_mul_kernel<float, float><<<blocks, 256, 0, s>>>((float*)x, (const float*)gate, gate_stride, rows, C, rep);
 }
 
 void indexed_gemv(const void* w, const int* sel, const void* x, int bf, long x_stride, int M, int E, int O, int I, int act, void* out,

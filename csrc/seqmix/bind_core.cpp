@@ -18,7 +18,7 @@ Tensor short_conv(const Tensor& x, const Tensor& w, const c10::optional<Tensor>&
 }
 
 // rows of x ([rows, C], row stride free) → out [rows, C] contiguous; w float [C] or one number
-Tensor rms_norm(const Tensor& x, const Tensor& w, double eps, const c10::optional<Tensor>& gate, bool out_bf16) {
+Tensor rms_norm(const Tensor& x, const Tensor& w, double eps, const c10::optional<Tensor>& gate, bool out_bf16, bool center) {
     TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1, "x must be [rows, C] with a contiguous last dimension");
     const int rows = x.size(0), C = x.size(1);
     TORCH_CHECK(w.numel() == 1 || w.numel() == C, "weight must hold 1 or C numbers");
@@ -32,20 +32,20 @@ Tensor rms_norm(const Tensor& x, const Tensor& w, double eps, const c10::optiona
     }
     if (rows)
         seqmix::rms_norm(x.data_ptr(), is_bf(x), x.stride(0), rows, C, f32(w), w.numel() == 1 ? 0 : 1, (float)eps, g, gs, out.data_ptr(),
-                         out_bf16, C, nullptr, 0, stream());
+                         out_bf16, C, nullptr, 0, center, stream());
     check_launch();
     return out;
 }
 
 // res [rows, C] float += norm(y) * w
-void add_rms_norm_(Tensor res, const Tensor& y, const Tensor& w, double eps) {
+void add_rms_norm_(Tensor res, const Tensor& y, const Tensor& w, double eps, bool center) {
     TORCH_CHECK(y.is_cuda() && y.dim() == 2 && y.stride(1) == 1 && res.dim() == 2 && res.stride(1) == 1 && res.scalar_type() == at::kFloat,
                 "res must be float [rows, C], y [rows, C]");
     const int rows = y.size(0), C = y.size(1);
     TORCH_CHECK(res.size(0) == rows && res.size(1) == C && (w.numel() == 1 || w.numel() == C), "shape mismatch");
     if (rows)
         seqmix::rms_norm(y.data_ptr(), is_bf(y), y.stride(0), rows, C, f32(w), w.numel() == 1 ? 0 : 1, (float)eps, nullptr, 0, nullptr, 0, 0,
-                         res.data_ptr<float>(), res.stride(0), stream());
+                         res.data_ptr<float>(), res.stride(0), center, stream());
     check_launch();
 }
 
@@ -114,14 +114,14 @@ Tensor embed_sinusoid(const Tensor& tokens, const Tensor& table, double scale, c
 
 // x [rows, C], gate [rows, C] (row strides free), w float [C] or [C / groups] → out [rows, C] (row stride free) of the gate's dtype
 void group_rms_norm_gated(const Tensor& x, const Tensor& gate, const Tensor& w, int64_t groups, double eps, bool gate_first, Tensor out,
-                          double out_scale) {
+                          double out_scale, bool sigmoid_gate) {
     TORCH_CHECK(x.is_cuda() && x.dim() == 2 && gate.dim() == 2 && out.dim() == 2 && x.stride(1) == 1 && gate.stride(1) == 1 && out.stride(1) == 1,
                 "x, gate, out must be [rows, C] with contiguous last dimensions");
     const int rows = x.size(0), C = x.size(1);
     TORCH_CHECK(gate.size(0) == rows && gate.size(1) == C && out.size(0) == rows && out.size(1) == C && groups >= 1 && C % groups == 0 &&
                     (w.numel() == C || w.numel() == C / groups) && out.scalar_type() == gate.scalar_type(), "shape mismatch");
     seqmix::group_rms_norm_gated(x.data_ptr(), is_bf(x), x.stride(0), gate.data_ptr(), is_bf(gate), gate.stride(0), f32(w), (int)w.numel(), rows,
-                                 C, (int)groups, (float)eps, gate_first, out.data_ptr(), out.stride(0), (float)out_scale, stream());
+                                 C, (int)groups, (float)eps, gate_first, out.data_ptr(), out.stride(0), (float)out_scale, sigmoid_gate, stream());
     check_launch();
 }
 
@@ -150,7 +150,41 @@ Tensor small_linear_f32(const Tensor& x, const Tensor& w) {
     return out;
 }
 
+// gu [M, 2F] contiguous → g sigmoid(slope g) (u + 1) with g = min(gu[:, :F], limit), u = clamp(gu[:, F:], -limit, limit)
+Tensor clamped_glu(const Tensor& gu, double limit, double slope) {
+    TORCH_CHECK(gu.is_cuda() && gu.dim() == 2 && gu.is_contiguous() && gu.size(1) % 2 == 0, "gu must be contiguous [M, 2F]");
+    Tensor out = at::empty({gu.size(0), gu.size(1) / 2}, gu.options());
+    seqmix::clamped_glu(gu.data_ptr(), out.data_ptr(), is_bf(gu), gu.size(0), (int)(gu.size(1) / 2), (float)limit, (float)slope, stream());
+    check_launch();
+    return out;
+}
+
+// x [N, C] contiguous *= sigmoid(gate [N, Cg]) with C % Cg == 0 (gate: bfloat16 or float, row stride free)
+void sigmoid_gate_mul_(Tensor x, const Tensor& gate) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && gate.dim() == 2 && gate.stride(1) == 1 && gate.size(0) == x.size(0) &&
+                    gate.size(1) > 0 && x.size(1) % gate.size(1) == 0, "x must be contiguous [N, C], gate [N, Cg] with Cg dividing C");
+    seqmix::sigmoid_gate_mul(x.data_ptr(), is_bf(x), gate.data_ptr(), is_bf(gate), gate.stride(0), x.size(0), (int)x.size(1),
+                             (int)(x.size(1) / gate.size(1)), stream());
+    check_launch();
+}
+
+// p [B,S,C] (last dim contiguous): hq query heads and hk key heads of D numbers, then the rest → float [B,S,C]
+Tensor rotary_qkv_f32(const Tensor& p, int64_t hq, int64_t hk, int64_t D, int64_t dims, const Tensor& inv_freq, const Tensor& pos0,
+                      double q_scale, double k_scale) {
+    TORCH_CHECK(p.is_cuda() && p.dim() == 3 && p.stride(2) == 1, "p must be [B,S,C] with a contiguous last dimension");
+    const int B = p.size(0), S = p.size(1), C = p.size(2);
+    TORCH_CHECK((hq + hk) * D <= C && dims % 2 == 0 && dims <= D && inv_freq.numel() == dims / 2 && pos0.numel() == B, "bad rotary sizes");
+    Tensor out = at::empty({B, S, C}, p.options().dtype(at::kFloat));
+    seqmix::rotary_qkv_f32(p.data_ptr(), is_bf(p), p.stride(0), p.stride(1), B, S, C, (int)hq, (int)hk, (int)D, (int)dims, f32(inv_freq),
+                           i32(pos0), (float)q_scale, (float)k_scale, out.data_ptr<float>(), stream());
+    check_launch();
+    return out;
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("clamped_glu", &clamped_glu);
+    m.def("sigmoid_gate_mul_", &sigmoid_gate_mul_);
+    m.def("rotary_qkv_f32", &rotary_qkv_f32);
     m.def("route_topk", &route_topk);
     m.def("small_linear_f32", &small_linear_f32);
     m.def("short_conv", &short_conv);

@@ -12,8 +12,8 @@ struct FloatProducts {
     ~FloatProducts() { at::globalContext().setAllowTF32CuBLAS(was); }
 };
 
-static Tensor gla_scan_chunked(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& z, const Tensor& zbias, double tau,
-                               Tensor state, const Tensor& slots, const Tensor& lens, bool fresh) {
+static Tensor gla_scan_chunked(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& z, const float* zbias, double tau,
+                               float qscale, const float* decay, Tensor state, const Tensor& slots, const Tensor& lens, bool fresh) {
     const int B = q.size(0), S = q.size(1), H = q.size(2), D = q.size(3), V = v.size(3), C = seqmix::gla_chunk_tokens();
     const auto f = q.options().dtype(at::kFloat);
     const long es = q.element_size();
@@ -31,8 +31,8 @@ static Tensor gla_scan_chunked(const Tensor& q, const Tensor& k, const Tensor& v
         Tensor Vf = at::empty({n, C, V}, f), A = at::empty({n, C, C}, f);
         const char *qp = (const char*)q.data_ptr() + s0 * q.stride(1) * es, *kp = (const char*)k.data_ptr() + s0 * k.stride(1) * es;
         const char *vp = (const char*)v.data_ptr() + s0 * v.stride(1) * es, *zp = (const char*)z.data_ptr() + s0 * z.stride(1) * es;
-        seqmix::gla_chunk_prep(qp, kp, vp, is_bf(q), q.stride(0), q.stride(1), zp, z.stride(0), z.stride(1), f32(zbias), (float)(1.0 / tau),
-                               (float)(1.0 / std::sqrt((double)D)), i32(lens_g), B, Sg, H, D, V, nC, Qe.data_ptr<float>(),
+        seqmix::gla_chunk_prep(qp, kp, vp, is_bf(q), q.stride(0), q.stride(1), zp, z.stride(0), z.stride(1), zbias, (float)(1.0 / tau),
+                               qscale, decay, i32(lens_g), B, Sg, H, D, V, nC, Qe.data_ptr<float>(),
                                Ke.data_ptr<float>(), Bc.data_ptr<float>(), G.data_ptr<float>(), Vf.data_ptr<float>(), A.data_ptr<float>(),
                                stream());
         check_launch();
@@ -46,8 +46,8 @@ static Tensor gla_scan_chunked(const Tensor& q, const Tensor& k, const Tensor& v
     return out;
 }
 
-Tensor gla_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& z, const Tensor& zbias, double tau, Tensor state,
-                const Tensor& slots, const Tensor& lens, bool fresh) {
+static Tensor linear_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& z, const float* zbias, double tau, float qscale,
+                          const float* decay, Tensor state, const Tensor& slots, const Tensor& lens, bool fresh) {
     TORCH_CHECK(q.is_cuda() && q.dim() == 4 && v.dim() == 4 && q.stride(3) == 1 && k.stride(3) == 1 && v.stride(3) == 1 && z.stride(2) == 1,
                 "bad recurrence operands");
     const int B = q.size(0), S = q.size(1), H = q.size(2), D = q.size(3), V = v.size(3);
@@ -58,20 +58,32 @@ Tensor gla_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor&
     TORCH_CHECK(state.is_contiguous() && state.scalar_type() == at::kFloat && state.size(1) == H && state.size(2) == D && state.size(3) == V,
                 "state must be float [slots,H,D,V]");
     TORCH_CHECK(q.scalar_type() == k.scalar_type() && q.scalar_type() == v.scalar_type() && q.scalar_type() == z.scalar_type(), "dtype mismatch");
-    if (S >= kGlaChunkedFrom) return gla_scan_chunked(q, k, v, z, zbias, tau, state, slots, lens, fresh);
+    if (S >= kGlaChunkedFrom) return gla_scan_chunked(q, k, v, z, zbias, tau, qscale, decay, state, slots, lens, fresh);
     Tensor out = at::empty({B, S, H, V}, q.options().dtype(at::kFloat));
-    if (S == 1 && seqmix::gla_step(q.data_ptr(), k.data_ptr(), v.data_ptr(), is_bf(q), q.stride(0), z.data_ptr(), z.stride(0), f32(zbias),
-                                   (float)(1.0 / tau), (float)(1.0 / std::sqrt((double)D)), state.data_ptr<float>(), i32(slots), i32(lens),
+    if (S == 1 && seqmix::gla_step(q.data_ptr(), k.data_ptr(), v.data_ptr(), is_bf(q), q.stride(0), z.data_ptr(), z.stride(0), zbias,
+                                   (float)(1.0 / tau), qscale, decay, state.data_ptr<float>(), i32(slots), i32(lens),
                                    fresh, B, H, D, V, out.data_ptr<float>(), stream())) {
         check_launch();
         return out;
     }
     bool ok = seqmix::gla_scan(q.data_ptr(), k.data_ptr(), v.data_ptr(), is_bf(q), q.stride(0), q.stride(1), z.data_ptr(), z.stride(0),
-                               z.stride(1), f32(zbias), (float)(1.0 / tau), (float)(1.0 / std::sqrt((double)D)), state.data_ptr<float>(),
+                               z.stride(1), zbias, (float)(1.0 / tau), qscale, decay, state.data_ptr<float>(),
                                i32(slots), i32(lens), fresh, B, S, H, D, V, out.data_ptr<float>(), stream());
-    TORCH_CHECK(ok, "gla_scan: no launch shape for key size ", D, " and value size ", V);
+    TORCH_CHECK(ok, "linear scan: no launch shape for key size ", D, " and value size ", V);
     check_launch();
     return out;
+}
+
+Tensor gla_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& z, const Tensor& zbias, double tau, Tensor state,
+                const Tensor& slots, const Tensor& lens, bool fresh) {
+    return linear_scan(q, k, v, z, f32(zbias), tau, (float)(1.0 / std::sqrt((double)q.size(3))), nullptr, state, slots, lens, fresh);
+}
+
+// Retention: the same scans with ONE fixed decay per head (decay float [H]) and no scale on the queries; q stands in for the unused z.
+Tensor retention_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& decay, Tensor state, const Tensor& slots,
+                      const Tensor& lens, bool fresh) {
+    TORCH_CHECK(q.dim() == 4 && decay.numel() == q.size(2), "one decay per head");
+    return linear_scan(q, k, v, q.flatten(2), nullptr, 1.0, 1.f, f32(decay), state, slots, lens, fresh);
 }
 
 // u [B,S,W] contiguous, gr / gi float [blocks, B*S, W/blocks], y [B,S,W] view (pre-activation) → out [B,S,W]; state [slots, W] float
@@ -90,5 +102,6 @@ Tensor rglru_scan(const Tensor& u, const Tensor& gr, const Tensor& gi, const Ten
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gla_scan", &gla_scan);
+    m.def("retention_scan", &retention_scan);
     m.def("rglru_scan", &rglru_scan);
 }

@@ -17,12 +17,26 @@ Tensor gated_delta_scan(const Tensor& q, const Tensor& k, const Tensor& v, const
                 "heads must be laid out one after another");
     same_tokens(q, k, "q and k");
     TORCH_CHECK(q.scalar_type() == k.scalar_type() && q.scalar_type() == v.scalar_type(), "dtype mismatch");
-    TORCH_CHECK(braw.scalar_type() == at::kFloat && araw.scalar_type() == at::kFloat && braw.dim() == 3 && araw.sizes() == braw.sizes() &&
-                    braw.size(2) == H && braw.stride(2) == 1 && araw.stride(2) == 1, "beta / decay pre-activations must be float [B,S,H]");
-    same_tokens(braw, araw, "beta and decay pre-activations");
     TORCH_CHECK(state.is_contiguous() && state.scalar_type() == at::kFloat && state.size(1) == H && state.size(2) == D && state.size(3) == V,
                 "state must be float [slots,H,D,V]");
     Tensor out = at::empty({B, S, H, V}, q.options().dtype(at::kFloat));
+    TORCH_CHECK(braw.scalar_type() == at::kFloat && araw.scalar_type() == at::kFloat && braw.dim() == 3 && braw.size(0) == B &&
+                    braw.size(1) == S && braw.size(2) == H && braw.stride(2) == 1, "beta pre-activations must be float [B,S,H]");
+    if (araw.dim() == 4) {                       // a decay per head and key channel
+        TORCH_CHECK(araw.size(0) == B && araw.size(1) == S && araw.size(2) == H && araw.size(3) == D && araw.stride(3) == 1 &&
+                        (H == 1 || araw.stride(2) == D) && dt_bias.numel() == (long)H * D && a_log.numel() == H,
+                    "decay pre-activations per channel must be float [B,S,H,D], dt_bias [H*D]");
+        bool okc = seqmix::gated_delta_channel_scan(q.data_ptr(), k.data_ptr(), q.stride(0), q.stride(1), v.data_ptr(), v.stride(0), v.stride(1),
+                                                    is_bf(q), braw.data_ptr<float>(), braw.stride(0), braw.stride(1), araw.data_ptr<float>(),
+                                                    araw.stride(0), araw.stride(1), f32(a_log), f32(dt_bias), state.data_ptr<float>(), i32(slots),
+                                                    i32(lens), fresh, B, S, H, G, D, V, (float)(1.0 / std::sqrt((double)D)),
+                                                    out.data_ptr<float>(), stream());
+        TORCH_CHECK(okc, "gated_delta_scan: key size ", D, " does not fit");
+        check_launch();
+        return out;
+    }
+    TORCH_CHECK(araw.sizes() == braw.sizes() && araw.stride(2) == 1 && dt_bias.numel() == H, "decay pre-activations must be float [B,S,H]");
+    same_tokens(braw, araw, "beta and decay pre-activations");
     bool ok = seqmix::gated_delta_scan(q.data_ptr(), k.data_ptr(), q.stride(0), q.stride(1), v.data_ptr(), v.stride(0), v.stride(1), is_bf(q),
                                        braw.data_ptr<float>(), araw.data_ptr<float>(), braw.stride(0), braw.stride(1), f32(a_log),
                                        f32(dt_bias), state.data_ptr<float>(), i32(slots), i32(lens), fresh, B, S, H, G, D, V,

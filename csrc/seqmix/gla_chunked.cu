@@ -23,16 +23,18 @@ int gla_chunk_tokens() { return kC; }
 template <typename T>
 __global__ void gla_chunk_prep_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long sb, long st,
                                       const T* __restrict__ z, long z_sb, long z_st, const float* __restrict__ zbias, float inv_tau2,
-                                      float qscale, const int* __restrict__ lens, int S, int H, int D, int V, float* __restrict__ Qe,
-                                      float* __restrict__ Ke, float* __restrict__ Bc, float* __restrict__ G, float* __restrict__ Vf) {
+                                      float qscale, const float* __restrict__ decay, const int* __restrict__ lens, int S, int H, int D, int V,
+                                      float* __restrict__ Qe, float* __restrict__ Ke, float* __restrict__ Bc, float* __restrict__ G,
+                                      float* __restrict__ Vf) {
     const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z, nC = gridDim.x;
     const int len = min(lens[b], S), t0 = c * kC, n = max(0, min(kC, len - t0));
     const long blk = ((long)b * H + h) * nC + c;
     float* qe = Qe + blk * kC * D;
     float* ke = Ke + blk * kC * D;
     float* bc = Bc + blk * kC * D;
+    const float fixed = decay ? log2f(decay[h]) : 0.f;     // a fixed decay per head: the same log-decay for every token and channel
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        const float zb = zbias[h * D + d];
+        const float zb = decay ? 0.f : zbias[h * D + d];
         const T* zp = z + (long)b * z_sb + (long)t0 * z_st + h * D + d;
         const T* qp = q + (long)b * sb + (long)t0 * st + h * D + d;
         const T* kp = k + (long)b * sb + (long)t0 * st + h * D + d;
@@ -41,7 +43,7 @@ __global__ void gla_chunk_prep_kernel(const T* __restrict__ q, const T* __restri
         for (int t = 0; t < kC; ++t) {
             float qv = 0.f;
             if (t < n) {
-                cum += log_sigmoidf_(ldf(zp + (long)t * z_st) + zb) * inv_tau2;
+                cum += decay ? fixed : log_sigmoidf_(ldf(zp + (long)t * z_st) + zb) * inv_tau2;
                 qv = ldf(qp + (long)t * st) * qscale * exp2f(cum);
             }
             bc[t * D + d] = cum;
@@ -135,18 +137,18 @@ __global__ void gla_carry_kernel(float* __restrict__ Sl, const float* __restrict
 }
 
 void gla_chunk_prep(const void* q, const void* k, const void* v, int bf, long sb, long st, const void* z, long z_sb, long z_st,
-                    const float* zbias, float inv_tau, float qscale, const int* lens, int B, int S, int H, int D, int V, int chunks,
-                    float* Qe, float* Ke, float* Bc, float* G, float* Vf, float* A, cudaStream_t s) {
+                    const float* zbias, float inv_tau, float qscale, const float* decay, const int* lens, int B, int S, int H, int D, int V,
+                    int chunks, float* Qe, float* Ke, float* Bc, float* G, float* Vf, float* A, cudaStream_t s) {
     dim3 grid(chunks, H, B);
     const int threads = D >= 256 ? 256 : (D > 64 ? 128 : 64);
     const float inv_tau2 = inv_tau * kLog2e;
     if (bf) {
         gla_chunk_prep_kernel<bf16><<<grid, threads, 0, s>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, sb, st, (const bf16*)z, z_sb,
-                                                            z_st, zbias, inv_tau2, qscale, lens, S, H, D, V, Qe, Ke, Bc, G, Vf);
+                                                            z_st, zbias, inv_tau2, qscale, decay, lens, S, H, D, V, Qe, Ke, Bc, G, Vf);
         gla_intra_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)q, (const bf16*)k, sb, st, Bc, qscale, lens, S, H, D, A);
     } else {
         gla_chunk_prep_kernel<float><<<grid, threads, 0, s>>>((const float*)q, (const float*)k, (const float*)v, sb, st, (const float*)z,
-                                                             z_sb, z_st, zbias, inv_tau2, qscale, lens, S, H, D, V, Qe, Ke, Bc, G, Vf);
+                                                             z_sb, z_st, zbias, inv_tau2, qscale, decay, lens, S, H, D, V, Qe, Ke, Bc, G, Vf);
         gla_intra_kernel<float><<<grid, 256, 0, s>>>((const float*)q, (const float*)k, sb, st, Bc, qscale, lens, S, H, D, A);
     }
 }

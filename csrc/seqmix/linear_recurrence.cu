@@ -1,6 +1,8 @@
 // Gated linear recurrences carried from token to token, states in float.
 //   gla_scan  : per head S_t = diag(alpha_t) S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t, with a decay per KEY channel
-//               alpha = sigmoid(z + bias)^(1/tau) = exp(log_sigmoid(z + bias) / tau), formed here in float from the projected z.
+//               alpha = sigmoid(z + bias)^(1/tau) = exp(log_sigmoid(z + bias) / tau), formed here in float from the projected z;
+//               with `decay` given (one number per head) alpha is that number for every token and channel (retention) and z is
+//               not read.
 //               A block owns one (sequence, head, slice of value columns); a thread owns DPT rows of one state column in registers;
 //               the step's alpha / k / q / v are staged through shared memory (double buffered: one barrier per token).
 //   rglru_scan: per channel  a = exp(-8 r softplus(lam)),  h_t = a h_(t-1) + sqrt(1 - a^2) i u_t,  out = h_t * gelu_tanh(y)
@@ -18,8 +20,9 @@ constexpr int kSteps = 8;   // tokens staged per barrier
 template <typename T, int DPT>
 __global__ void gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long sb, long st,
                                 const T* __restrict__ z, long z_sb, long z_st, const float* __restrict__ zbias, float inv_tau,
-                                float qscale, float* state, const int* __restrict__ slots, const int* __restrict__ lens, int fresh,
-                                int S, int H, int D, int V, int R, int Vb, int TB, float* __restrict__ out) {
+                                float qscale, const float* __restrict__ decay, float* state, const int* __restrict__ slots,
+                                const int* __restrict__ lens, int fresh, int S, int H, int D, int V, int R, int Vb, int TB,
+                                float* __restrict__ out) {
     extern __shared__ float4 sm4[];
     float* sm = reinterpret_cast<float*>(sm4);
     const int h = blockIdx.x, b = blockIdx.y, j0 = blockIdx.z * Vb;
@@ -50,7 +53,7 @@ __global__ void gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k
             if (x < 3 * nD) {
                 const int pl = x / nD, idx = tid + (x - pl * nD) * nthr;
                 const int u = idx / D, d = idx - u * D, t = min(t0 + u, len - 1);
-                if (u < TB) stage[x] = pl == 0 ? ldf(zp + (long)t * z_st + d) : ldf((pl == 1 ? kp : qp) + (long)t * st + d);
+                if (u < TB) stage[x] = pl == 0 ? (decay ? 0.f : ldf(zp + (long)t * z_st + d)) : ldf((pl == 1 ? kp : qp) + (long)t * st + d);
             } else if (x < 3 * nD + nV) {
                 const int idx = tid + (x - 3 * nD) * nthr;
                 const int u = idx / Vb, jj = idx - u * Vb, t = min(t0 + u, len - 1);
@@ -66,7 +69,7 @@ __global__ void gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k
                 const int u = idx / D, d = idx - u * D;
                 if (u < TB) {
                     float val = stage[x];
-                    if (pl == 0) val = 1.f + expm1f(log_sigmoidf_(val + zbias[hq + d]) * inv_tau);   // one rounding of an accurate value
+                    if (pl == 0) val = decay ? decay[h] : 1.f + expm1f(log_sigmoidf_(val + zbias[hq + d]) * inv_tau);   // one rounding of an accurate value
                     else if (pl == 2) val *= qscale;
                     dst[u * per + 4 * d + pl] = val;
                 }
@@ -120,8 +123,8 @@ static int pow2ceil(int x) { int p = 1; while (p < x) p <<= 1; return p; }
 
 template <typename T>
 static bool gla_launch(const void* q, const void* k, const void* v, long sb, long st, const void* z, long z_sb, long z_st,
-                       const float* zbias, float inv_tau, float qscale, float* state, const int* slots, const int* lens, int fresh,
-                       int B, int S, int H, int D, int V, float* out, cudaStream_t s) {
+                       const float* zbias, float inv_tau, float qscale, const float* decay, float* state, const int* slots,
+                       const int* lens, int fresh, int B, int S, int H, int D, int V, float* out, cudaStream_t s) {
     // fewer, fatter blocks (more state rows per thread) as long as the grid still fills the GPU: the step's alpha / k / q are
     // prepared once per block, so every extra slice of value columns repeats that work
     const int dpts[3] = {32, 16, 8};
@@ -150,7 +153,7 @@ static bool gla_launch(const void* q, const void* k, const void* v, long sb, lon
     do {                                                                                                                          \
         cudaFuncSetAttribute(gla_scan_kernel<T, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);                      \
         gla_scan_kernel<T, P><<<grid, threads, smem, s>>>((const T*)q, (const T*)k, (const T*)v, sb, st, (const T*)z, z_sb, z_st,    \
-                                                          zbias, inv_tau, qscale, state, slots, lens, fresh, S, H, D, V, R, Vb, TB, out); \
+                                                          zbias, inv_tau, qscale, decay, state, slots, lens, fresh, S, H, D, V, R, Vb, TB, out); \
     } while (0)
     if (pick == 8) SEQMIX_GLA(8); else if (pick == 16) SEQMIX_GLA(16); else SEQMIX_GLA(32);
 #undef SEQMIX_GLA
@@ -158,10 +161,10 @@ static bool gla_launch(const void* q, const void* k, const void* v, long sb, lon
 }
 
 bool gla_scan(const void* q, const void* k, const void* v, int bf, long sb, long st, const void* z, long z_sb, long z_st,
-              const float* zbias, float inv_tau, float qscale, float* state, const int* slots, const int* lens, int fresh, int B, int S,
-              int H, int D, int V, float* out, cudaStream_t s) {
-    return bf ? gla_launch<bf16>(q, k, v, sb, st, z, z_sb, z_st, zbias, inv_tau, qscale, state, slots, lens, fresh, B, S, H, D, V, out, s)
-              : gla_launch<float>(q, k, v, sb, st, z, z_sb, z_st, zbias, inv_tau, qscale, state, slots, lens, fresh, B, S, H, D, V, out, s);
+              const float* zbias, float inv_tau, float qscale, const float* decay, float* state, const int* slots, const int* lens,
+              int fresh, int B, int S, int H, int D, int V, float* out, cudaStream_t s) {
+    return bf ? gla_launch<bf16>(q, k, v, sb, st, z, z_sb, z_st, zbias, inv_tau, qscale, decay, state, slots, lens, fresh, B, S, H, D, V, out, s)
+              : gla_launch<float>(q, k, v, sb, st, z, z_sb, z_st, zbias, inv_tau, qscale, decay, state, slots, lens, fresh, B, S, H, D, V, out, s);
 }
 
 // One new token per sequence (token generation): the step is bound by reading and writing the state once, so a block owns 64
@@ -172,8 +175,8 @@ constexpr int kStepCols = 64, kStepGroups = 4, kStepUnroll = 8;
 template <typename T>
 __global__ void __launch_bounds__(kStepCols* kStepGroups)
 gla_step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long sb, const T* __restrict__ z, long z_sb,
-                const float* __restrict__ zbias, float inv_tau, float qscale, float* state, const int* __restrict__ slots,
-                const int* __restrict__ lens, int fresh, int H, int D, int V, float* __restrict__ out) {
+                const float* __restrict__ zbias, float inv_tau, float qscale, const float* __restrict__ decay, float* state,
+                const int* __restrict__ slots, const int* __restrict__ lens, int fresh, int H, int D, int V, float* __restrict__ out) {
     extern __shared__ float sm[];              // alpha [D], k [D], q [D], sums [groups][cols]
     float *sa = sm, *sk = sm + D, *sq = sm + 2 * D, *red = sm + 3 * D;
     const int h = blockIdx.y, b = blockIdx.z, tid = threadIdx.x, jl = tid % kStepCols, g = tid / kStepCols;
@@ -186,7 +189,7 @@ gla_step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     }
     const long hq = (long)h * D;
     for (int d = tid; d < D; d += kStepCols * kStepGroups) {
-        sa[d] = 1.f + expm1f(log_sigmoidf_(ldf(z + (long)b * z_sb + hq + d) + zbias[hq + d]) * inv_tau);
+        sa[d] = decay ? decay[h] : 1.f + expm1f(log_sigmoidf_(ldf(z + (long)b * z_sb + hq + d) + zbias[hq + d]) * inv_tau);
         sk[d] = ldf(k + (long)b * sb + hq + d);
         sq[d] = ldf(q + (long)b * sb + hq + d) * qscale;
     }
@@ -223,20 +226,20 @@ gla_step_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
 
 template <typename T>
 static void gla_step_launch(const void* q, const void* k, const void* v, long sb, const void* z, long z_sb, const float* zbias,
-                            float inv_tau, float qscale, float* state, const int* slots, const int* lens, int fresh, int B, int H, int D,
+                            float inv_tau, float qscale, const float* decay, float* state, const int* slots, const int* lens, int fresh, int B, int H, int D,
                             int V, float* out, cudaStream_t s) {
     dim3 grid((V + kStepCols - 1) / kStepCols, H, B);
     const size_t smem = (size_t)(3 * D + kStepGroups * kStepCols) * sizeof(float);
     gla_step_kernel<T><<<grid, kStepCols * kStepGroups, smem, s>>>((const T*)q, (const T*)k, (const T*)v, sb, (const T*)z, z_sb, zbias, inv_tau,
-                                                                  qscale, state, slots, lens, fresh, H, D, V, out);
+                                                                  qscale, decay, state, slots, lens, fresh, H, D, V, out);
 }
 
 bool gla_step(const void* q, const void* k, const void* v, int bf, long sb, const void* z, long z_sb, const float* zbias, float inv_tau,
-              float qscale, float* state, const int* slots, const int* lens, int fresh, int B, int H, int D, int V, float* out,
+              float qscale, const float* decay, float* state, const int* slots, const int* lens, int fresh, int B, int H, int D, int V, float* out,
               cudaStream_t s) {
     if ((size_t)(3 * D + kStepGroups * kStepCols) * sizeof(float) > 48 * 1024) return false;
-    if (bf) gla_step_launch<bf16>(q, k, v, sb, z, z_sb, zbias, inv_tau, qscale, state, slots, lens, fresh, B, H, D, V, out, s);
-    else gla_step_launch<float>(q, k, v, sb, z, z_sb, zbias, inv_tau, qscale, state, slots, lens, fresh, B, H, D, V, out, s);
+    if (bf) gla_step_launch<bf16>(q, k, v, sb, z, z_sb, zbias, inv_tau, qscale, decay, state, slots, lens, fresh, B, H, D, V, out, s);
+    else gla_step_launch<float>(q, k, v, sb, z, z_sb, zbias, inv_tau, qscale, decay, state, slots, lens, fresh, B, H, D, V, out, s);
     return true;
 }
 

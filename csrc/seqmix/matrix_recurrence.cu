@@ -3,6 +3,9 @@
 //                      q and k are made unit vectors here (x / sqrt(sum x^2 + 1e-6), q also times D^-1/2); beta = sigmoid(braw),
 //                      g = exp(-exp(a_log) softplus(araw + dt_bias)).  With A = M_old^T k and Bq = M_old^T q one pass over the old
 //                      state gives u = beta (v - g A) and o = g Bq + (k.q) u, and the update M = g M_old + k u^T follows in registers.
+//   gated_delta_scan with a decay per KEY CHANNEL (araw / dt_bias hold D numbers per head): g is a vector that scales the rows of M.
+//                      With gk = g * k and gq = g * q (coordinate by coordinate), A = M_old^T gk and Bq = M_old^T gq give
+//                      u = beta (v - A), o = Bq + (k.q) u and M = diag(g) M_old + k u^T: four staged vectors per token instead of two.
 //   ssd_scan         : dt = softplus(dtraw + dt_bias);  M <- exp(-exp(a_log) dt) M + dt b x^T;  y = M^T c + dskip x   (M [N, V])
 // A block owns 32 value columns of one (sequence, head): lane = column, warp = one of 8 row groups, a thread keeps DPT consecutive
 // rows of its column in registers (rows past the state's size are zeros that never change), so state loads and stores are whole
@@ -117,6 +120,130 @@ __global__ void __launch_bounds__(256) gated_delta_kernel(
             if (r == 0 && col) out[(((long)b * S + t0 + u) * H + h) * V + j] = fmaf(g, Bq, kq * uv);
 #pragma unroll
             for (int i = 0; i < DPT; ++i) M[i] = fmaf(g, M[i], kr[i] * uv);
+        }
+    }
+    if (col) {
+        for (int t = len + r; t < S; t += kRowGroups) out[(((long)b * S + t) * H + h) * V + j] = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = r * DPT + i;
+            if (d < D && (len > 0 || fresh)) sp[(long)d * V + j] = M[i];
+        }
+    }
+}
+
+// The delta rule with one decay per head and key channel.  Same block shape and staging as gated_delta_kernel; araw [B,S,H,D] float
+// (strides a_sb, a_st; heads one after another), dt_bias [H*D].
+template <typename T, int DPT>
+__global__ void __launch_bounds__(256) gated_delta_channel_kernel(
+    const T* __restrict__ q, const T* __restrict__ k, long qk_sb, long qk_st, const T* __restrict__ v, long v_sb, long v_st,
+    const float* __restrict__ braw, long b_sb, long b_st, const float* __restrict__ araw, long a_sb, long a_st,
+    const float* __restrict__ a_log, const float* __restrict__ dt_bias, float* state, const int* __restrict__ slots,
+    const int* __restrict__ lens, int fresh, int S, int H, int G, int D, int V, float qscale, float* __restrict__ out) {
+    extern __shared__ float sm[];
+    constexpr int Dp = DPT * kRowGroups;         // padded row count (>= D); rows past D hold zeros
+    float* sk = sm;                              // [kTok][Dp] unit keys
+    float* sg = sk + kTok * Dp;                  // [kTok][Dp] decays
+    float* sgk = sg + kTok * Dp;                 // [kTok][Dp] decay * unit key
+    float* sgq = sgk + kTok * Dp;                // [kTok][Dp] decay * unit query * qscale
+    float* sv = sgq + kTok * Dp;                 // [kTok][kCols]
+    float* sc = sv + kTok * kCols;               // [kTok][4]: beta, k.q
+    float* part = sc + kTok * 4;                 // [2][2][kRowGroups][kCols]
+    const int h = blockIdx.x, b = blockIdx.y, j0 = blockIdx.z * kCols;
+    const int lane = threadIdx.x & 31, r = threadIdx.x >> 5, j = j0 + lane;
+    const int len = min(lens[b], S), hk = h / (H / G);
+    const bool col = j < V;
+    float* sp = state + (((long)slots[b] * H + h) * D) * V;
+    float M[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = r * DPT + i;
+        M[i] = (!fresh && col && d < D) ? sp[(long)d * V + j] : 0.f;
+    }
+    for (int x = threadIdx.x; x < 4 * kTok * Dp; x += 256) sm[x] = 0.f;       // the padding rows stay zero
+    const float ea = expf(a_log[h]);
+    constexpr int DL = DPT >= 4 ? DPT / 4 : 1;   // key coordinates per lane: D <= 8 DPT = 32 DL
+    float qraw[DL], kraw[DL], araw_[DL], db[DL], vraw = 0.f, braw_ = 0.f;
+#pragma unroll
+    for (int i = 0; i < DL; ++i) { const int d = lane + 32 * i; db[i] = d < D ? dt_bias[(long)h * D + d] : 0.f; }
+    auto fetch = [&](int t) {
+        if (t < len) {
+            const T* qp = q + (long)b * qk_sb + (long)t * qk_st + (long)hk * D;
+            const T* kp = k + (long)b * qk_sb + (long)t * qk_st + (long)hk * D;
+            const float* ap = araw + (long)b * a_sb + (long)t * a_st + (long)h * D;
+#pragma unroll
+            for (int i = 0; i < DL; ++i) {
+                const int d = lane + 32 * i;
+                qraw[i] = d < D ? ldf(qp + d) : 0.f;
+                kraw[i] = d < D ? ldf(kp + d) : 0.f;
+                araw_[i] = d < D ? ap[d] : 0.f;
+            }
+            vraw = col ? ldf(v + (long)b * v_sb + (long)t * v_st + (long)h * V + j) : 0.f;
+            braw_ = braw[(long)b * b_sb + (long)t * b_st + h];
+        }
+    };
+    fetch(r);
+    for (int t0 = 0; t0 < len; t0 += kTok) {
+        __syncthreads();                         // the previous chunk's tokens are consumed
+        if (t0 + r < len) {
+            float qq = 0.f, kk = 0.f, qk = 0.f;
+#pragma unroll
+            for (int i = 0; i < DL; ++i) { qq = fmaf(qraw[i], qraw[i], qq); kk = fmaf(kraw[i], kraw[i], kk); qk = fmaf(qraw[i], kraw[i], qk); }
+            qq = warp_sum(qq); kk = warp_sum(kk); qk = warp_sum(qk);
+            const float iq = qscale / sqrtf(qq + 1e-6f), ik = 1.f / sqrtf(kk + 1e-6f);
+#pragma unroll
+            for (int i = 0; i < DL; ++i) {
+                const int d = lane + 32 * i;
+                if (d < D) {
+                    const float g = expf(-ea * softplusf_(araw_[i] + db[i])), ku = kraw[i] * ik;
+                    sk[r * Dp + d] = ku;
+                    sg[r * Dp + d] = g;
+                    sgk[r * Dp + d] = g * ku;
+                    sgq[r * Dp + d] = g * (qraw[i] * iq);
+                }
+            }
+            sv[r * kCols + lane] = vraw;
+            if (lane == 0) {
+                sc[r * 4 + 0] = sigmoidf_(braw_);
+                sc[r * 4 + 1] = qk * iq * ik;
+            }
+        }
+        __syncthreads();
+        fetch(t0 + kTok + r);
+        const int nt = min(kTok, len - t0);
+        for (int u = 0; u < nt; ++u) {
+            const float* ku = sk + u * Dp + r * DPT;
+            const float* gu = sg + u * Dp + r * DPT;
+            const float* gku = sgk + u * Dp + r * DPT;
+            const float* gqu = sgq + u * Dp + r * DPT;
+            float kr[DPT], gr[DPT];
+            float A = 0.f, Bq = 0.f;
+            if (DPT >= 4) {
+#pragma unroll
+                for (int i = 0; i < DPT; i += 4) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(ku + i), g4 = *reinterpret_cast<const float4*>(gu + i);
+                    const float4 a4 = *reinterpret_cast<const float4*>(gku + i), q4 = *reinterpret_cast<const float4*>(gqu + i);
+                    kr[i] = k4.x; kr[i + 1] = k4.y; kr[i + 2] = k4.z; kr[i + 3] = k4.w;
+                    gr[i] = g4.x; gr[i + 1] = g4.y; gr[i + 2] = g4.z; gr[i + 3] = g4.w;
+                    A = fmaf(M[i], a4.x, fmaf(M[i + 1], a4.y, fmaf(M[i + 2], a4.z, fmaf(M[i + 3], a4.w, A))));
+                    Bq = fmaf(M[i], q4.x, fmaf(M[i + 1], q4.y, fmaf(M[i + 2], q4.z, fmaf(M[i + 3], q4.w, Bq))));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) { kr[i] = ku[i]; gr[i] = gu[i]; A = fmaf(M[i], gku[i], A); Bq = fmaf(M[i], gqu[i], Bq); }
+            }
+            float* pb = part + ((t0 + u) & 1) * 2 * kRowGroups * kCols;
+            pb[r * kCols + lane] = A;
+            pb[(kRowGroups + r) * kCols + lane] = Bq;
+            __syncthreads();
+            A = 0.f; Bq = 0.f;
+#pragma unroll
+            for (int w = 0; w < kRowGroups; ++w) { A += pb[w * kCols + lane]; Bq += pb[(kRowGroups + w) * kCols + lane]; }
+            const float beta = sc[u * 4], kq = sc[u * 4 + 1];
+            const float uv = beta * (sv[u * kCols + lane] - A);
+            if (r == 0 && col) out[(((long)b * S + t0 + u) * H + h) * V + j] = fmaf(kq, uv, Bq);
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) M[i] = fmaf(gr[i], M[i], kr[i] * uv);
         }
     }
     if (col) {
@@ -263,6 +390,37 @@ bool gated_delta_scan(const void* q, const void* k, long qk_sb, long qk_st, cons
     }
 #undef SEQMIX_GDR_T
 #undef SEQMIX_GDR
+    return true;
+}
+
+bool gated_delta_channel_scan(const void* q, const void* k, long qk_sb, long qk_st, const void* v, long v_sb, long v_st, int bf,
+                              const float* braw, long b_sb, long b_st, const float* araw, long a_sb, long a_st, const float* a_log,
+                              const float* dt_bias, float* state, const int* slots, const int* lens, int fresh, int B, int S, int H, int G,
+                              int D, int V, float qscale, float* out, cudaStream_t s) {
+    const int dpt = rows_per_thread(D);
+    if (!dpt) return false;
+    if (B == 0 || S == 0) return true;
+    dim3 grid(H, B, (V + kCols - 1) / kCols), block(256);
+    const size_t smem = sizeof(float) * (4 * kTok * dpt * kRowGroups + kTok * kCols + kTok * 4 + 2 * 2 * kRowGroups * kCols);
+#define SEQMIX_GDC(T, P)                                                                                                              \
+    do {                                                                                                                              \
+        cudaFuncSetAttribute(gated_delta_channel_kernel<T, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);               \
+        gated_delta_channel_kernel<T, P><<<grid, block, smem, s>>>((const T*)q, (const T*)k, qk_sb, qk_st, (const T*)v, v_sb, v_st, braw,  \
+                                                                   b_sb, b_st, araw, a_sb, a_st, a_log, dt_bias, state, slots, lens, fresh, \
+                                                                   S, H, G, D, V, qscale, out);                                       \
+    } while (0)
+#define SEQMIX_GDC_T(P) do { if (bf) SEQMIX_GDC(bf16, P); else SEQMIX_GDC(float, P); } while (0)
+    switch (dpt) {
+        case 1: SEQMIX_GDC_T(1); break;
+        case 2: SEQMIX_GDC_T(2); break;
+        case 4: SEQMIX_GDC_T(4); break;
+        case 8: SEQMIX_GDC_T(8); break;
+        case 16: SEQMIX_GDC_T(16); break;
+        case 32: SEQMIX_GDC_T(32); break;
+        default: SEQMIX_GDC_T(64); break;
+    }
+#undef SEQMIX_GDC_T
+#undef SEQMIX_GDC
     return true;
 }
 

@@ -1,4 +1,5 @@
-// RMS norms of the sequence-mixer models: y = x / sqrt(mean(x^2) + eps) * w with w a vector or ONE number for all coordinates,
+// RMS norms of the sequence-mixer models: y = x / sqrt(mean(x^2) + eps) * w with w a vector or ONE number for all coordinates
+// (with `center`, x's mean is taken off first: a layer norm with a gain and no bias, two passes over the row for the statistics),
 // optionally times silu(gate), written out or accumulated into a float residual stream (x_res += norm(y): the residual sum of a
 // layer that normalises the sublayer's OUTPUT).  Statistics in float.
 #include "seq_common.cuh"
@@ -12,36 +13,54 @@ namespace seqmix {
 template <typename Tin, typename Tout, bool VEC>
 __global__ void rms_norm_kernel(const Tin* __restrict__ x, long x_stride, int rows, int C, const float* __restrict__ w, int w_stride,
                                 float eps, const Tout* __restrict__ gate, long gate_stride, Tout* __restrict__ out, long out_stride,
-                                float* res, long res_stride) {
+                                float* res, long res_stride, int center) {
     __shared__ float part[8];
     const int row = blockIdx.x * blockDim.y + threadIdx.y, tx = threadIdx.x, TX = blockDim.x;
     const bool on = row < rows;
     const Tin* xr = x + (long)(on ? row : 0) * x_stride;
+    auto row_sum = [&](float v) {               // over the threads that share the row
+        v = warp_sum(v);
+        if (TX > 32) {                          // one row per block: fold the warps' sums
+            __syncthreads();
+            if ((tx & 31) == 0) part[tx >> 5] = v;
+            __syncthreads();
+            v = 0.f;
+            for (int k = 0; k < TX / 32; ++k) v += part[k];
+        }
+        return v;
+    };
+    float mean = 0.f;
+    if (center) {
+        float sx = 0.f;
+        if (on) {
+            if (VEC) {
+                for (int c = tx * 4; c < C; c += TX * 4) { const float4 v = ld4(xr + c); sx += (v.x + v.y) + (v.z + v.w); }
+            } else {
+                for (int c = tx; c < C; c += TX) sx += ldf(xr + c);
+            }
+        }
+        mean = row_sum(sx) / (float)C;
+    }
     float ss = 0.f;
     if (on) {
         if (VEC) {
             for (int c = tx * 4; c < C; c += TX * 4) {
-                const float4 v = ld4(xr + c);
+                float4 v = ld4(xr + c);
+                v.x -= mean; v.y -= mean; v.z -= mean; v.w -= mean;
                 ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
             }
         } else {
-            for (int c = tx; c < C; c += TX) { float v = ldf(xr + c); ss = fmaf(v, v, ss); }
+            for (int c = tx; c < C; c += TX) { float v = ldf(xr + c) - mean; ss = fmaf(v, v, ss); }
         }
     }
-    ss = warp_sum(ss);
-    if (TX > 32) {                              // one row per block: fold the warps' sums
-        if ((tx & 31) == 0) part[tx >> 5] = ss;
-        __syncthreads();
-        ss = 0.f;
-        for (int k = 0; k < TX / 32; ++k) ss += part[k];
-    }
+    ss = row_sum(ss);
     if (!on) return;
     const float inv = 1.f / sqrtf(ss / (float)C + eps);
     if (VEC) {
         for (int c = tx * 4; c < C; c += TX * 4) {
             float4 v = ld4(xr + c);
             const float4 g = w_stride ? ld4(w + c) : make_float4(w[0], w[0], w[0], w[0]);
-            v = make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+            v = make_float4((v.x - mean) * inv * g.x, (v.y - mean) * inv * g.y, (v.z - mean) * inv * g.z, (v.w - mean) * inv * g.w);
             if (gate) {
                 const float4 t = ld4(gate + (long)row * gate_stride + c);
                 v.x *= t.x * sigmoidf_(t.x); v.y *= t.y * sigmoidf_(t.y); v.z *= t.z * sigmoidf_(t.z); v.w *= t.w * sigmoidf_(t.w);
@@ -55,7 +74,7 @@ __global__ void rms_norm_kernel(const Tin* __restrict__ x, long x_stride, int ro
         return;
     }
     for (int c = tx; c < C; c += TX) {
-        float v = ldf(xr + c) * inv * w[(long)c * w_stride];
+        float v = (ldf(xr + c) - mean) * inv * w[(long)c * w_stride];
         if (gate) { float g = ldf(gate + (long)row * gate_stride + c); v *= g * sigmoidf_(g); }
         if (res) res[(long)row * res_stride + c] += v;
         else stf(out + (long)row * out_stride + c, v);
@@ -69,7 +88,9 @@ __global__ void rms_norm_kernel(const Tin* __restrict__ x, long x_stride, int ro
 template <typename Tin, typename Tg, bool VEC>
 __global__ void group_rms_norm_gated_kernel(const Tin* __restrict__ x, long x_stride, const Tg* __restrict__ gate, long gate_stride,
                                             const float* __restrict__ w, int wn, int rows, int C, int groups, float eps, int gate_first,
-                                            Tg* __restrict__ out, long out_stride, float out_scale) {
+                                            Tg* __restrict__ out, long out_stride, float out_scale, int sigmoid_gate) {
+    // the gate's factor: silu(z) = z sigmoid(z), or sigmoid(z) alone
+    auto gf = [&](float z) { return (sigmoid_gate ? 1.f : z) * sigmoidf_(z); };
     __shared__ float part[8];
     const long unit = (long)blockIdx.x * blockDim.y + threadIdx.y;
     const bool on = unit < (long)rows * groups;
@@ -84,14 +105,14 @@ __global__ void group_rms_norm_gated_kernel(const Tin* __restrict__ x, long x_st
                 float4 v = ld4(xr + c);
                 if (gate_first) {
                     const float4 z = ld4(gr + c);
-                    v.x *= z.x * sigmoidf_(z.x); v.y *= z.y * sigmoidf_(z.y); v.z *= z.z * sigmoidf_(z.z); v.w *= z.w * sigmoidf_(z.w);
+                    v.x *= gf(z.x); v.y *= gf(z.y); v.z *= gf(z.z); v.w *= gf(z.w);
                 }
                 ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
             }
         } else {
             for (int c = tx; c < Cg; c += TX) {
                 float v = ldf(xr + c);
-                if (gate_first) { const float z = ldf(gr + c); v *= z * sigmoidf_(z); }
+                if (gate_first) { const float z = ldf(gr + c); v *= gf(z); }
                 ss = fmaf(v, v, ss);
             }
         }
@@ -110,20 +131,19 @@ __global__ void group_rms_norm_gated_kernel(const Tin* __restrict__ x, long x_st
     if (VEC) {
         for (int c = tx * 4; c < Cg; c += TX * 4) {
             const float4 v = ld4(xr + c), z = ld4(gr + c), u = ld4(wr + c);
-            st4(o + c, make_float4(v.x * (z.x * sigmoidf_(z.x)) * inv * u.x, v.y * (z.y * sigmoidf_(z.y)) * inv * u.y,
-                                   v.z * (z.z * sigmoidf_(z.z)) * inv * u.z, v.w * (z.w * sigmoidf_(z.w)) * inv * u.w));
+            st4(o + c, make_float4(v.x * gf(z.x) * inv * u.x, v.y * gf(z.y) * inv * u.y, v.z * gf(z.z) * inv * u.z, v.w * gf(z.w) * inv * u.w));
         }
         return;
     }
     for (int c = tx; c < Cg; c += TX) {
         const float z = ldf(gr + c);
-        stf(o + c, ldf(xr + c) * (z * sigmoidf_(z)) * inv * wr[c]);
+        stf(o + c, ldf(xr + c) * gf(z) * inv * wr[c]);
     }
 }
 
 void group_rms_norm_gated(const void* x, int in_bf16, long x_stride, const void* gate, int gate_bf16, long gate_stride, const float* w,
                           int wn, int rows, int C, int groups, float eps, int gate_first, void* out, long out_stride, float out_scale,
-                          cudaStream_t s) {
+                          int sigmoid_gate, cudaStream_t s) {
     const long units = (long)rows * groups;
     if (units == 0) return;
     const int Cg = C / groups;
@@ -134,7 +154,7 @@ void group_rms_norm_gated(const void* x, int in_bf16, long x_stride, const void*
                      (uintptr_t)gate % (4 * eg) == 0 && (uintptr_t)out % (4 * eg) == 0 && (uintptr_t)w % 16 == 0;
 #define SEQMIX_GN_V(TI, TG, V)                                                                                                        \
     group_rms_norm_gated_kernel<TI, TG, V><<<grid, block, 0, s>>>((const TI*)x, x_stride, (const TG*)gate, gate_stride, w, wn, rows, C,  \
-                                                                  groups, eps, gate_first, (TG*)out, out_stride, out_scale)
+                                                                  groups, eps, gate_first, (TG*)out, out_stride, out_scale, sigmoid_gate)
 #define SEQMIX_GN(TI, TG) do { if (vec) SEQMIX_GN_V(TI, TG, true); else SEQMIX_GN_V(TI, TG, false); } while (0)
     if (in_bf16 && gate_bf16) SEQMIX_GN(bf16, bf16);
     else if (!in_bf16 && gate_bf16) SEQMIX_GN(float, bf16);
@@ -145,7 +165,7 @@ void group_rms_norm_gated(const void* x, int in_bf16, long x_stride, const void*
 }
 
 void rms_norm(const void* x, int in_bf16, long x_stride, int rows, int C, const float* w, int w_stride, float eps, const void* gate,
-              long gate_stride, void* out, int out_bf16, long out_stride, float* res, long res_stride, cudaStream_t s) {
+              long gate_stride, void* out, int out_bf16, long out_stride, float* res, long res_stride, int center, cudaStream_t s) {
     const bool few = rows < 148 * 8 && C >= 512;
     dim3 block(few ? 256 : 32, few ? 1 : 8), grid(few ? rows : (rows + 7) / 8);
     const size_t ei = in_bf16 ? 2 : 4, eo = out_bf16 ? 2 : 4;
@@ -154,7 +174,7 @@ void rms_norm(const void* x, int in_bf16, long x_stride, int rows, int C, const 
                      (!gate || gate_stride % 4 == 0) && al(out, eo) && (res || out_stride % 4 == 0) && al(res, 4) && (!res || res_stride % 4 == 0);
 #define SEQMIX_NORM_V(TI, TO, V)                                                                                                    \
     rms_norm_kernel<TI, TO, V><<<grid, block, 0, s>>>((const TI*)x, x_stride, rows, C, w, w_stride, eps, (const TO*)gate, gate_stride, \
-                                                      (TO*)out, out_stride, res, res_stride)
+                                                      (TO*)out, out_stride, res, res_stride, center)
 #define SEQMIX_NORM(TI, TO) do { if (vec) SEQMIX_NORM_V(TI, TO, true); else SEQMIX_NORM_V(TI, TO, false); } while (0)
     if (in_bf16 && out_bf16) SEQMIX_NORM(bf16, bf16);
     else if (!in_bf16 && out_bf16) SEQMIX_NORM(float, bf16);

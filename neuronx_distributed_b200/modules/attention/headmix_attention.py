@@ -12,7 +12,10 @@ coordinate with ``sigmoid(W_g h)`` and projected out.  ``temp``, ``talk`` and ``
 
 State per sequence: the convolution history of q|k and a ring of ``min(chunk, window)`` rotated key rows and value rows (position
 j sits in row ``j mod ring``; a chunk's first token overwrites the row of the previous chunk's first token, which it no longer sees).
-q, k and the gate are one stacked projection and ONE convolution runs over the q|k channels.  ``mix`` writes the gated heads into
+q, k and the gate are one stacked projection and ONE convolution runs over the q|k channels.  The mixing is linear in the queries, so
+the kernels move it onto them: head h's mixed query against key head c is ``Q'[h,c,:] = sum_{g in group c} talk[h,g] scale temp[g] q_g``
+and its score is one dot product of ``Q'[h]`` with the position's keys of all key heads side by side; after that the attention is an
+ordinary one with key size ``kv_heads * dim``.  ``mix`` writes the gated heads into
 a caller's buffer; ``forward`` is the stand-alone layer."""
 from __future__ import annotations
 
@@ -57,14 +60,13 @@ class HeadMixAttention(nn.Module):
         return {"conv": self.conv.state_spec(self.dtype), "k": ((self.ring, self.kv_heads, self.dim), self.dtype),
                 "v": ((self.ring, self.kv_heads, self.dim), self.dtype)}
 
-    def _score_coef(self) -> torch.Tensor:
-        """``scale * temp[h]``, formed once per set of weights."""
-        if self.temp is None:
-            key = None
-        else:
-            key = (self.temp.data_ptr(), self.temp._version)
+    def _mix_weights(self) -> torch.Tensor:
+        """``talk[h,g] * scale * temp[g]`` (float ``[H,H]``), formed once per set of weights."""
+        key = tuple((p.data_ptr(), p._version) for p in (self.temp, self.talk) if p is not None)
         if self._coef is None or self._coef[0] != key:
-            self._coef = (key, (self.unit if self.temp is None else self.temp.detach()) * self.scale)
+            coef = (self.unit if self.temp is None else self.temp.detach()) * self.scale
+            talk = torch.eye(self.heads, dtype=torch.float32, device=coef.device) if self.talk is None else self.talk.detach()
+            self._coef = (key, (talk * coef[None, :]).contiguous())
         return self._coef[1]
 
     def mix(self, h: torch.Tensor, ctx, st: Dict[str, torch.Tensor], out: torch.Tensor) -> torch.Tensor:
@@ -78,14 +80,13 @@ class HeadMixAttention(nn.Module):
         c = self.conv(p[..., :nqk], st["conv"], ctx, h.dtype)                        # [B,S,q|k]
         q = c[..., :self.n_q].unflatten(-1, (H, D))
         k = c[..., self.n_q:].unflatten(-1, (G, D))
-        rows = seqmix.headmix_qk_prepare(q, k, self.rot_dims, self.inv_freq, ctx.pos0, ctx.lens, ctx.slots, st["k"], st["v"],
-                                         want_rows=ctx.fresh)
+        qmix, rows = seqmix.headmix_qk_prepare(q, k, self._mix_weights(), self.rot_dims, self.inv_freq, ctx.pos0, ctx.lens, ctx.slots,
+                                               st["k"], st["v"], want_rows=ctx.fresh)
         gate = p[..., nqk:]
         if ctx.fresh:
-            return seqmix.headmix_attention_prompt(q, rows, k, self._score_coef(), self.talk, self.sink, gate, ctx.lens, self.chunk,
-                                                   self.window, out)
-        return seqmix.headmix_attention_token(q, st["k"], st["v"], self._score_coef(), self.talk, self.sink, gate, ctx.slots, ctx.pos0,
-                                              ctx.lens, self.chunk, self.window, out)
+            return seqmix.headmix_attention_prompt(qmix, rows, k, self.sink, gate, ctx.lens, self.chunk, self.window, out)
+        return seqmix.headmix_attention_token(qmix, st["k"], st["v"], self.sink, gate, ctx.slots, ctx.pos0, ctx.lens, self.chunk,
+                                              self.window, out)
 
     def forward(self, h: torch.Tensor, ctx, st: Dict[str, torch.Tensor]) -> torch.Tensor:
         B, S, _ = h.shape

@@ -28,7 +28,7 @@ CSRC = _ext.PKG_DIR.parent / "csrc" / "seqmix"
 # Kernel groups, each its own extension ``nxd_b200_seq_<group>_C`` built in-tree on first use, so that a model compiles only the
 # mechanisms it has: group → (sources, functions it exports).
 GROUPS = {
-    "core": (["short_conv.cu", "norms.cu", "activations.cu", "embed.cu", "bind_core.cpp"],
+    "core": (["short_conv.cu", "norms.cu", "activations.cu", "embed.cu", "rotary.cu", "bind_core.cpp"],
              ["short_conv", "rms_norm", "add_rms_norm_", "xielu", "gelu_erf", "silu_mul", "indexed_gemv", "moe_combine", "embed_sinusoid",
               "group_rms_norm_gated", "route_topk", "small_linear_f32", "clamped_glu", "sigmoid_gate_mul_", "rotary_qkv_f32"]),
     "latent": (["latent_attention.cu", "latent_decode.cu", "latent_prefill.cu", "bind_latent.cpp"],
@@ -698,20 +698,25 @@ def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: tor
 
 
 # -------------------------------------------------------------- softmax attention with scores mixed across heads and a sink term
-def headmix_qk_prepare(q: torch.Tensor, k: torch.Tensor, dims: int, inv_freq: torch.Tensor, pos0: torch.Tensor, lens: torch.Tensor,
-                       slots: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, want_rows: bool) -> Optional[torch.Tensor]:
-    """Queries and keys that double as values: ``q [B,S,H,D]``, ``k [B,S,G,D]`` (views; last dim contiguous).  The first ``dims``
-    coordinates of every query head are rotated IN PLACE (rotate-half pairs, in float, at positions ``pos0[b] + t``).  The keys as
-    they come are the VALUES; rotated the same way they are the KEYS.  The last ``ring`` real tokens of each row go to ``kcache``
-    (rotated) and ``vcache`` (as they come), both ``[slots, ring, G, D]``, at row ``position mod ring``; with ``want_rows`` the
-    rotated keys come back as ``[B,S,G,D]``."""
+# The mixing is linear in the queries, so it is moved onto them: with ``score_g = c_g q_g . k_kv(g)`` and ``s_h = sum_g T[h,g]
+# score_g``, head h's mixed query against key head c is ``Q'[h,c,:] = sum_{g in group c} T[h,g] c_g q_g`` and ``s_h = sum_c Q'[h,c,:] .
+# k_c``: one dot product of length G*D between head h's row of Q' and the position's keys with all key heads side by side.
+def headmix_qk_prepare(q: torch.Tensor, k: torch.Tensor, mixw: torch.Tensor, dims: int, inv_freq: torch.Tensor, pos0: torch.Tensor,
+                       lens: torch.Tensor, slots: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, want_rows: bool):
+    """Queries to be mixed across heads and keys that double as values: ``q [B,S,H,D]``, ``k [B,S,G,D]`` (views; last dim contiguous),
+    ``mixw [H,H]`` float (``T[h,g] * c_g``).  Queries and keys are rotated on their first ``dims`` coordinates (rotate-half pairs, in
+    float, at positions ``pos0[b] + t``).  Returns ``(Q' [B,S,H,G*D], rotated keys [B,S,G,D] or None)``.  The keys as they come are
+    the VALUES: the last ``ring`` real tokens of each row go to ``kcache`` (rotated) and ``vcache`` (as they come), both ``[slots,
+    ring, G, D]``, at row ``position mod ring``.  Rows past ``lens`` are left unwritten."""
     if _cuda(k):
         _ext.count_launch()
-        rows = ext().headmix_qk_prepare(q, k, dims, inv_freq, _i32(pos0), _i32(lens), _i32(slots), kcache, vcache, want_rows)
-        return rows if want_rows else None
-    B, S = k.shape[:2]
+        qmix, rows = ext().headmix_qk_prepare(q, k, mixw, dims, inv_freq, _i32(pos0), _i32(lens), _i32(slots), kcache, vcache, want_rows)
+        return qmix, (rows if want_rows else None)
+    B, S, H, D = q.shape
+    G = k.shape[2]
     pos = pos0.long()[:, None] + torch.arange(S)[None, :]
-    q.copy_(_rotate(q.float(), pos[:, :, None], inv_freq, dims).to(q.dtype))
+    qr = _rotate(q.float(), pos[:, :, None], inv_freq, dims).view(B, S, G, H // G, D)
+    qmix = torch.einsum("hcr,bscrd->bshcd", mixw.view(H, G, H // G), qr).reshape(B, S, H, G * D).to(q.dtype)
     rows = _rotate(k.float(), pos[:, :, None], inv_freq, dims).to(k.dtype)
     ring = kcache.shape[1]
     for b in range(B):
@@ -719,7 +724,7 @@ def headmix_qk_prepare(q: torch.Tensor, k: torch.Tensor, dims: int, inv_freq: to
         for t in range(max(0, n - ring), n):
             kcache[int(slots[b]), int(pos[b, t]) % ring] = rows[b, t]
             vcache[int(slots[b]), int(pos[b, t]) % ring] = k[b, t]
-    return rows if want_rows else None
+    return qmix, (rows if want_rows else None)
 
 
 def _visible(i: torch.Tensor, j: torch.Tensor, chunk: int, window: int) -> torch.Tensor:
@@ -731,10 +736,9 @@ def _visible(i: torch.Tensor, j: torch.Tensor, chunk: int, window: int) -> torch
     return ok
 
 
-def _headmix_softmax(raw: torch.Tensor, talk: Optional[torch.Tensor], sink: Optional[torch.Tensor], ok: torch.Tensor) -> torch.Tensor:
-    """``raw [B,H,Q,K]`` scaled scores, ``ok [B,1|H,Q,K]`` → weights: heads mixed by ``talk [H,H]``, softmax over the visible keys
-    whose denominator also holds ``exp(sink_h)``."""
-    sc = raw if talk is None else torch.einsum("hg,bgqk->bhqk", talk, raw)
+def _sink_softmax(sc: torch.Tensor, sink: Optional[torch.Tensor], ok: torch.Tensor) -> torch.Tensor:
+    """``sc [B,H,Q,K]`` scores, ``ok`` broadcastable → weights: softmax over the visible keys whose denominator also holds
+    ``exp(sink_h)``."""
     sc = sc.masked_fill(~ok, float("-inf"))
     if sink is not None:
         sc = torch.cat([sc, sink.view(1, -1, 1, 1).expand(sc.shape[0], -1, sc.shape[2], 1)], -1)
@@ -742,60 +746,58 @@ def _headmix_softmax(raw: torch.Tensor, talk: Optional[torch.Tensor], sink: Opti
     return p[..., :-1] if sink is not None else p
 
 
-def headmix_attention_prompt(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, coef: torch.Tensor, talk: Optional[torch.Tensor],
-                             sink: Optional[torch.Tensor], gate: Optional[torch.Tensor], lens: torch.Tensor, chunk: int, window: int,
-                             out: torch.Tensor) -> torch.Tensor:
-    """Prompts that start at position 0: ``q [B,S,H,D]``, ``k [B,S,G,D]``, ``v [B,S,G,V]`` (views); query head h uses key/value head
-    ``h // (H/G)``.  Score of head g: ``q_g . k * coef[g]`` (float); the heads' scores of a (query, key) pair are then mixed,
-    ``score_h = sum_g talk[h,g] score_g``.  Query i sees ``j <= i`` of its own aligned chunk of ``chunk`` positions (0: no chunks) and
-    within ``window`` positions back (0: no window).  Softmax in float with ``exp(sink[h])`` added to the denominator (no key, no
-    value).  The heads' results times ``sigmoid(gate [B,S,H*V])`` go to ``out [B*S, H*V]`` (row stride free); padded rows give
-    zeros."""
-    if _cuda(q):
+def headmix_attention_prompt(qmix: torch.Tensor, krows: torch.Tensor, v: torch.Tensor, sink: Optional[torch.Tensor],
+                             gate: Optional[torch.Tensor], lens: torch.Tensor, chunk: int, window: int, out: torch.Tensor) -> torch.Tensor:
+    """Prompts that start at position 0: mixed queries ``qmix [B,S,H,G*D]``, rotated keys ``krows [B,S,G,D]``, values ``v [B,S,G,D]``
+    (a view); head h reads value head ``h // (H/G)``.  Score of head h for (i, j): ``qmix[i,h] . krows[j]`` over all ``G*D`` numbers
+    (float).  Query i sees ``j <= i`` of its own aligned chunk of ``chunk`` positions (0: no chunks) and within ``window`` positions
+    back (0: no window).  Softmax in float with ``exp(sink[h])`` added to the denominator (no key, no value).  The heads' results
+    times ``sigmoid(gate [B,S,H*D])`` go to ``out [B*S, H*D]`` (row stride free); padded rows give zeros."""
+    if _cuda(qmix):
         _ext.count_launch()
-        ext().headmix_attention_prompt(q, k, v, coef, talk, sink, gate, _i32(lens), chunk, window, out)
+        ext().headmix_attention_prompt(qmix, krows, v, sink, gate, _i32(lens), chunk, window, out)
         return out
-    B, S, H, D = q.shape
-    G, V = k.shape[2], v.shape[3]
-    kk, vv = k.float().repeat_interleave(H // G, 2), v.float().repeat_interleave(H // G, 2)
-    raw = torch.einsum("bihd,bjhd->bhij", q.float(), kk) * coef.view(1, H, 1, 1)
+    B, S, H, DK = qmix.shape
+    G, D = krows.shape[2], krows.shape[3]
+    real = torch.arange(S)[None, :] < lens[:, None]
+    kk = torch.where(real[..., None], krows.float().reshape(B, S, DK), torch.zeros(()))              # padded rows hold anything
+    vv = torch.where(real[..., None, None], v.float(), torch.zeros(())).repeat_interleave(H // G, 2)
+    qq = torch.where(real[..., None, None], qmix.float(), torch.zeros(()))
+    sc = torch.einsum("bihx,bjx->bhij", qq, kk)
     i, j = torch.arange(S)[:, None], torch.arange(S)[None, :]
-    p = _headmix_softmax(raw, talk, sink, _visible(i, j, chunk, window)[None, None])
-    o = torch.einsum("bhij,bjhv->bihv", p, vv).reshape(B, S, H * V)
+    p = _sink_softmax(sc, sink, _visible(i, j, chunk, window)[None, None])
+    o = torch.einsum("bhij,bjhv->bihv", p, vv).reshape(B, S, H * D)
     if gate is not None:
         o = o * torch.sigmoid(gate.float())
-    o = torch.where((torch.arange(S)[None, :] < lens[:, None])[..., None], o, torch.zeros_like(o))
-    out[:, :H * V] = o.reshape(B * S, H * V).to(out.dtype)
+    o = torch.where(real[..., None], o, torch.zeros_like(o))
+    out[:, :H * D] = o.reshape(B * S, H * D).to(out.dtype)
     return out
 
 
-def headmix_attention_token(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, coef: torch.Tensor, talk: Optional[torch.Tensor],
-                            sink: Optional[torch.Tensor], gate: Optional[torch.Tensor], slots: torch.Tensor, pos0: torch.Tensor,
-                            lens: torch.Tensor, chunk: int, window: int, out: torch.Tensor) -> torch.Tensor:
-    """Single tokens ``q [B,1,H,D]`` at positions ``pos0`` against their slots' rings (``kcache [slots, ring, G, D]``, ``vcache
-    [slots, ring, G, V]``; row ``j mod ring`` holds position j, the token's own row included; the ring is at least as long as the
-    longest visible stretch).  Scores, mixing, sink, gate and output layout as :func:`headmix_attention_prompt`; rows with ``lens == 0``
-    give zeros."""
-    if _cuda(q):
+def headmix_attention_token(qmix: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, sink: Optional[torch.Tensor],
+                            gate: Optional[torch.Tensor], slots: torch.Tensor, pos0: torch.Tensor, lens: torch.Tensor, chunk: int, window: int,
+                            out: torch.Tensor) -> torch.Tensor:
+    """Single tokens' mixed queries ``qmix [B,1,H,G*D]`` at positions ``pos0`` against their slots' rings (``kcache, vcache [slots,
+    ring, G, D]``; row ``j mod ring`` holds position j, the token's own row included; the ring is at least as long as the longest
+    visible stretch).  Scores, sink, gate and output layout as :func:`headmix_attention_prompt`; rows with ``lens == 0`` give zeros."""
+    if _cuda(qmix):
         _ext.count_launch()
-        ext().headmix_attention_token(q, kcache, vcache, coef, talk, sink, gate, _i32(slots), _i32(pos0), _i32(lens), chunk, window, out)
+        ext().headmix_attention_token(qmix, kcache, vcache, sink, gate, _i32(slots), _i32(pos0), _i32(lens), chunk, window, out)
         return out
-    B, _, H, D = q.shape
-    ring, G, V = kcache.shape[1], kcache.shape[2], vcache.shape[3]
-    kb = kcache[slots.long()].float().repeat_interleave(H // G, 2)                                  # [B, ring, H, D]
-    vb = vcache[slots.long()].float().repeat_interleave(H // G, 2)
-    raw = torch.einsum("bhd,brhd->bhr", q[:, 0].float(), kb) * coef.view(1, H, 1)
+    B, _, H, DK = qmix.shape
+    ring, G, D = kcache.shape[1], kcache.shape[2], kcache.shape[3]
     p_ = pos0.long()[:, None]
     back = torch.remainder(p_ - torch.arange(ring)[None, :], ring)                                   # distance back of ring row r
     ok = _visible(p_, p_ - back, chunk, window)                                                      # [B, ring]
-    raw = torch.where(ok[:, None, :], raw, torch.zeros_like(raw))                                   # rows never written hold anything
-    vb = torch.where(ok[:, :, None, None], vb, torch.zeros_like(vb))
-    w = _headmix_softmax(raw[:, :, None, :], talk, sink, ok[:, None, None, :])[:, :, 0]             # [B,H,ring]
-    o = torch.einsum("bhr,brhv->bhv", w, vb).reshape(B, H * V)
+    kb = torch.where(ok[..., None], kcache[slots.long()].float().reshape(B, ring, DK), torch.zeros(()))   # rows never written hold anything
+    vb = torch.where(ok[..., None, None], vcache[slots.long()].float(), torch.zeros(())).repeat_interleave(H // G, 2)
+    sc = torch.einsum("bhx,brx->bhr", qmix[:, 0].float(), kb)
+    w = _sink_softmax(sc[:, :, None, :], sink, ok[:, None, None, :])[:, :, 0]                        # [B,H,ring]
+    o = torch.einsum("bhr,brhv->bhv", w, vb).reshape(B, H * D)
     if gate is not None:
-        o = o * torch.sigmoid(gate.float()).view(B, H * V)
+        o = o * torch.sigmoid(gate.float()).view(B, H * D)
     o = torch.where((lens > 0)[:, None], o, torch.zeros_like(o))
-    out[:, :H * V] = o.to(out.dtype)
+    out[:, :H * D] = o.to(out.dtype)
     return out
 
 
