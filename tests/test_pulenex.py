@@ -1,0 +1,713 @@
+"""Pulenex serving path against the plain oracle (tests/pulenex_oracle.py): every mechanism alone, whole prompts, prompt + token by
+token decoding, unequal batches, reused slots, chunk and window edges, the sink, far keys through the recurrent states, borrowed
+latents, other sizes, greedy generation through the serving entry points, the registry / checkpoint reader, the trace runner and
+the generation command line.  Configurations and weights are made here (random, seeded)."""
+import io
+import json
+import math
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import pulenex_oracle as oracle  # noqa: E402
+
+from neuronx_distributed_b200.inference.hf_adapter import HuggingFaceGenerationAdapter  # noqa: E402
+from neuronx_distributed_b200.inference.trace_replay import TraceReplayer  # noqa: E402
+from neuronx_distributed_b200.models import registry  # noqa: E402
+from neuronx_distributed_b200.models.pulenex import PulenexConfig, PulenexForInference, complete_config, load_pulenex_weights  # noqa: E402
+from neuronx_distributed_b200.modules.attention.utils import deinterleave_rows  # noqa: E402
+from neuronx_distributed_b200.ops import seqmix  # noqa: E402
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DEVICES = ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)]
+TOL32 = 2e-4
+
+
+# ------------------------------------------------------------------------------------------------------------------ model making
+def ffn(ff=40, limit=1.5):
+    return {"kind": "dense", "ff": ff, "limit": limit}
+
+
+def latent(heads=3, dim=16, rot_dim=8, vdim=24, kv_rank=20, window=7, base=5000.0, kv_from=None, mlp="default"):
+    m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "mask": {"size": window},
+         "rot": {"base": base, "dims": rot_dim}, "scale": 1.0 / math.sqrt(dim + rot_dim)}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return {"type": "latent_attention", "mixer": m, "mlp": ffn() if mlp == "default" else mlp}
+
+
+def retention(heads=3, dim=16, vdim=24, dims=12, decay=None, base=30000.0, mlp=None):
+    decay = decay or [1.0 - 2.0 ** (-3 - 1.5 * h) for h in range(heads)]
+    return {"type": "retention", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "decay": decay, "rot": {"base": base, "dims": dims}}, "mlp": mlp}
+
+
+def left_spec(heads=4, kv_heads=2, dim=16, conv=3, chunk=9, dims=8, base=800.0):
+    return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "conv": conv, "mask": {"size": chunk}, "rot": {"base": base, "dims": dims},
+            "scale": 1.0 / math.sqrt(dim)}
+
+
+def right_spec(heads=4, kv_heads=2, dim=12, vdim=20, conv=2):
+    return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv}
+
+
+def par(left=None, right=None, mlp="default"):
+    return {"type": "parallel", "mixer": {"left": left or left_spec(), "right": right or right_spec()}, "mlp": ffn() if mlp == "default" else mlp}
+
+
+def make_cfg(layers, vocab=50, width=48, eps=1e-5, logit_scale=0.7):
+    return {"architecture": "Pulenex", "vocab": vocab, "width": width, "norm": {"eps": eps}, "logit_scale": logit_scale, "layers": layers}
+
+
+def random_checkpoint(cfg, seed=0, ranks=(5, 7)):
+    g = torch.Generator().manual_seed(seed)
+    bf = lambda t: t.to(torch.bfloat16).float()
+    lin = lambda o, i, s=1.0: bf(torch.randn(o, i, generator=g) * s / math.sqrt(i))
+    vec = lambda n, s=1.0, m=0.0: bf(torch.randn(n, generator=g) * s + m)
+    W, w = cfg["width"], {}
+    w["embed"], w["head"], w["final.norm"] = bf(torch.randn(cfg["vocab"], W, generator=g)), lin(cfg["vocab"], W), vec(W, 0.2, 1.0)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        for n in ("norm1", "norm1b"):
+            w[p + n] = vec(W, 0.2, 1.0)
+        q = p + "mix."
+        if L["type"] == "latent_attention":
+            H, D, R, V, C = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            w.update({q + "q": lin(H * (D + R), W, 2.0), q + "uk": lin(H * D, C, 2.0), q + "uv": lin(H * V, C), q + "g": lin(H, W, 2.0), q + "o": lin(W, H * V)})
+            if m.get("kv_from") is None:
+                w.update({q + "dkv": lin(C + R, W, 2.0), q + "dkv.norm": vec(C, 0.3, 1.0)})
+        elif L["type"] == "retention":
+            H, D, V = m["heads"], m["dim"], m["vdim"]
+            w.update({q + "q": lin(H * D, W, 2.0), q + "k": lin(H * D, W, 2.0), q + "v": lin(H * V, W), q + "g": lin(H * V, W), q + "o": lin(W, H * V)})
+        else:
+            a, b = m["left"], m["right"]
+            H, G, D, taps = a["heads"], a["kv_heads"], a["dim"], a["conv"]
+            l = q + "left."
+            w.update({l + "q": lin(H * D, W, 2.0), l + "k": lin(G * D, W, 2.0), l + "q.conv": bf(torch.randn(H * D, taps, generator=g) * 0.6),
+                      l + "k.conv": bf(torch.randn(G * D, taps, generator=g) * 0.6), l + "talk": bf(torch.eye(H) + torch.randn(H, H, generator=g) * 0.4),
+                      l + "temp": vec(H, 0.3, 1.2), l + "sink": vec(H, 1.0), l + "g": lin(H * D, W), l + "o": lin(W, H * D), l + "out": vec(W, 0.2, 1.0)})
+            H, G, D, V, taps = b["heads"], b["kv_heads"], b["dim"], b["vdim"], b["conv"]
+            r = q + "right."
+            w.update({r + "q": lin(G * D, W, 2.0), r + "k": lin(G * D, W, 2.0), r + "v": lin(H * V, W, 2.0),
+                      r + "q.conv": bf(torch.randn(G * D, taps, generator=g) * 0.6), r + "k.conv": bf(torch.randn(G * D, taps, generator=g) * 0.6),
+                      r + "v.conv": bf(torch.randn(H * V, taps, generator=g) * 0.6), r + "b": lin(H, W, 2.0), r + "a1": lin(ranks[0], W, 2.0),
+                      r + "a2": lin(H * D, ranks[0], 2.0), r + "g1": lin(ranks[1], W, 2.0), r + "g2": lin(H * V, ranks[1], 2.0),
+                      r + "A_log": vec(H, 0.5, -1.0), r + "dt_bias": vec(H * D, 0.5), r + "norm": vec(V, 0.2, 1.0), r + "o": lin(W, H * V),
+                      r + "out": vec(W, 0.2, 1.0)})
+        f = L.get("mlp")
+        if not f:
+            continue
+        for n in ("norm2", "norm2b"):
+            w[p + n] = vec(W, 0.2, 1.0)
+        y = p + "mlp."
+        w.update({y + "gate": lin(f["ff"], W, 2.0), y + "gate.b": vec(f["ff"], 0.3), y + "up": lin(f["ff"], W, 2.0), y + "up.b": vec(f["ff"], 0.3),
+                  y + "down": lin(W, f["ff"]), y + "down.b": vec(W, 0.3)})
+    return w
+
+
+def build(cfg, weights, device, dtype=torch.float32, max_seq_len=4096, batch_size=1):
+    full = complete_config(cfg, {k: tuple(v.shape) for k, v in weights.items()})
+    m = PulenexForInference(PulenexConfig.from_dict(full, dtype=dtype, device=torch.device(device)), batch_size=batch_size,
+                            max_seq_len=max_seq_len, on_device_sampling=False)
+    load_pulenex_weights(m.lm, weights)
+    return m.eval()
+
+
+def tokens_for(cfg, n, seed):
+    return torch.randint(0, cfg["vocab"], (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def run_alone(model, toks, prompt):
+    """Prompt of ``prompt`` tokens in one step, the rest one by one → logits at every position [S, vocab] (float, cpu)."""
+    mgr = model.states
+    slot = mgr.alloc()
+    dev = next(model.parameters()).device
+    x = model.forward_step(torch.tensor([toks[:prompt]], device=dev), [prompt], [slot], [0], True)
+    out = [model.logits(x[0])]
+    for p in range(prompt, len(toks)):
+        x = model.forward_step(torch.tensor([[toks[p]]], device=dev), [1], [slot], [p], False)
+        out.append(model.logits(x[0]))
+    mgr.free(slot)
+    return torch.cat(out).cpu()
+
+
+def close(got, want, tol):
+    """Mean-free difference relative to the spread of the expected values, per position."""
+    d = got.double() - want.double()
+    d = d - d.mean(-1, keepdim=True)
+    ref = (want - want.mean(-1, keepdim=True)).double().pow(2).mean().sqrt()
+    err = (d.pow(2).mean(-1).sqrt() / ref).max().item()
+    assert err < tol, f"relative error {err:.3e} >= {tol}"
+
+
+def i32(v, device):
+    return torch.tensor(v, dtype=torch.int32, device=device)
+
+
+# ------------------------------------------------------------------------------------------------------------ single mechanisms
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("rows,C", [(7, 48), (3, 37), (300, 64), (2, 1024), (5, 1030)])
+def test_gain_only_layer_norm_and_its_residual_form(device, rows, C):
+    g = torch.Generator().manual_seed(C)
+    x, w = torch.randn(rows, C, generator=g) * 3 + 2, torch.randn(C, generator=g) * 0.3 + 1       # a mean well away from zero
+    want = oracle.centred_norm(x.double(), w.double(), 1e-5)
+    got = seqmix.rms_norm(x.to(device), w.to(device), 1e-5, None, torch.float32, center=True).cpu()
+    assert (got.double() - want).abs().max() < 2e-5
+    assert (got.double() - oracle.rms(x.double(), 1e-5) * w.double()).abs().max() > 1e-2              # not the uncentred norm
+    res = torch.randn(rows, C, generator=g)
+    got = seqmix.add_rms_norm_(res.clone().to(device), x.to(device), w.to(device), 1e-5, center=True).cpu()
+    assert (got.double() - (res.double() + want)).abs().max() < 2e-5
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("M,F,limit", [(5, 7, 1.0), (40, 64, 2.5), (3, 33, 0.5)])
+def test_clamped_gated_activation(device, M, F, limit):
+    g = torch.Generator().manual_seed(M * F)
+    gu = torch.randn(M, 2 * F, generator=g) * 2                                                     # both clamps bite
+    gd, ud = gu[:, :F].double().clamp(max=limit), gu[:, F:].double().clamp(-limit, limit)
+    want = gd * oracle.sigmoid(1.702 * gd) * (ud + 1)
+    assert (gu[:, :F] < -limit).any() and (gu[:, :F] > limit).any() and (gu[:, F:] < -limit).any()
+    assert (seqmix.clamped_glu(gu.to(device), limit, 1.702).cpu().double() - want).abs().max() < 1e-6
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("N,H,V", [(5, 3, 8), (40, 1, 33), (3, 6, 1)])
+def test_sigmoid_output_gates_per_head_and_per_coordinate(device, N, H, V):
+    g = torch.Generator().manual_seed(N * H)
+    x, per_head, big = torch.randn(N, H * V, generator=g), torch.randn(N, H, generator=g), torch.randn(N, H * V + 6, generator=g)
+    got = seqmix.sigmoid_gate_mul_(x.clone().to(device), per_head.to(device)).cpu()
+    assert (got.double() - (x.double().view(N, H, V) * oracle.sigmoid(per_head.double())[..., None]).view(N, -1)).abs().max() < 1e-6
+    got = seqmix.sigmoid_gate_mul_(x.clone().to(device), big.to(device)[:, 3:3 + H * V]).cpu()     # a strided view
+    assert (got.double() - x.double() * oracle.sigmoid(big[:, 3:3 + H * V].double())).abs().max() < 1e-6
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("rows,C,groups", [(7, 48, 4), (70, 40, 1), (3, 66, 2)])
+def test_grouped_norm_with_a_sigmoid_gate(device, rows, C, groups):
+    g = torch.Generator().manual_seed(rows)
+    x, gate, w = torch.randn(rows, C, generator=g), torch.randn(rows, C, generator=g), torch.randn(C // groups, generator=g)
+    got = seqmix.group_rms_norm_gated(x.to(device), gate.to(device), w.to(device), groups, 1e-5, False, out_dtype=torch.float32,
+                                      gate_act="sigmoid").cpu()
+    want = (oracle.rms(x.double().view(rows, groups, -1), 1e-5) * w.double()).reshape(rows, C) * oracle.sigmoid(gate.double())
+    assert (got.double() - want).abs().max() < 1e-5
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("H,D,V,dims", [(3, 16, 24, 12), (2, 8, 8, 8), (1, 20, 3, 2)])
+def test_float_rotation_of_a_stacked_projection(device, H, D, V, dims):
+    g = torch.Generator().manual_seed(H * D)
+    B, S, base = 2, 9, 700.0
+    p = torch.randn(B, S, 2 * H * D + H * V + 5, generator=g)
+    pos0 = [0, 300]
+    got = seqmix.rotary_qkv_f32(p.to(device)[..., :2 * H * D + H * V], H, H, D, dims, seqmix.rotary_inv_freq(dims, base, device),
+                                i32(pos0, device), 1.0, 0.25).cpu()
+    for b in range(B):
+        q = oracle.rotate(p[b, :, :H * D].double().view(S, H, D), dims, base, False, pos0[b])
+        k = oracle.rotate(p[b, :, H * D:2 * H * D].double().view(S, H, D), dims, base, False, pos0[b]) * 0.25
+        want = torch.cat([q.reshape(S, -1), k.reshape(S, -1), p[b, :, 2 * H * D:2 * H * D + H * V].double()], -1)
+        assert (got[b].double() - want).abs().max() < 2e-4                  # float angles at positions in the hundreds
+
+
+def test_deinterleaved_rows_give_the_same_scores():
+    """Rotation over neighbouring pairs equals rotation over the two halves once the rows of both projections are reordered."""
+    g = torch.Generator().manual_seed(4)
+    H, D, off, dims, S, W = 3, 14, 4, 8, 6, 10
+    wq, wk, h = torch.randn(H * D, W, generator=g).double(), torch.randn(H * D, W, generator=g).double(), torch.randn(S, W, generator=g).double()
+
+    def scores(wq, wk, interleaved):
+        q, k = (h @ wq.T).view(S, H, D), (h @ wk.T).view(S, H, D)
+        q = torch.cat([q[..., :off], oracle.rotate(q[..., off:], dims, 100.0, interleaved)], -1)
+        k = torch.cat([k[..., :off], oracle.rotate(k[..., off:], dims, 100.0, interleaved)], -1)
+        return torch.einsum("ihd,jhd->hij", q, k)
+
+    want = scores(wq, wk, True)
+    got = scores(deinterleave_rows(wq, H, D, off, dims), deinterleave_rows(wk, H, D, off, dims), False)
+    assert (got - want).abs().max() < 1e-10 and (scores(wq, wk, False) - want).abs().max() > 1e-3
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("H,D,V,S", [(3, 16, 24, 21), (2, 64, 64, 150), (1, 9, 70, 40), (4, 33, 5, 70)])
+def test_retention_scan_rows_of_many_lengths_and_a_carried_state(device, H, D, V, S):
+    """Prompts of unequal lengths (the long ones take the chunked form), then single tokens from the carried state."""
+    g = torch.Generator().manual_seed(H * D)
+    B, extra = 3, 5
+    lens = [S, 1, S // 2]
+    f = torch.randn(B, S + extra, 2 * H * D + H * V, generator=g)
+    decay = torch.tensor([1.0 - 2.0 ** (-2 - 2 * h) for h in range(H)])
+    cut = lambda t: (t[..., :H * D].unflatten(-1, (H, D)), t[..., H * D:2 * H * D].unflatten(-1, (H, D)) * 0.3, t[..., 2 * H * D:].unflatten(-1, (H, V)))
+    want = []
+    for b in range(B):
+        n = lens[b] + extra
+        q, k, v = (t.double() for t in cut(f[b, :n]))
+        o = torch.zeros(n, H, V, dtype=torch.float64)
+        for h in range(H):
+            M = torch.zeros(D, V, dtype=torch.float64)
+            for t in range(n):
+                M = decay[h].double() * M + torch.outer(k[t, h], v[t, h])
+                o[t, h] = M.T @ q[t, h]
+        want.append(o)
+    state = torch.full((5, H, D, V), float("nan"), device=device)          # whatever a slot held must never be read
+    slots = i32([4, 0, 2], device)
+    got = seqmix.retention_scan(*cut(f[:, :S].to(device)), decay.to(device), state, slots, i32(lens, device), True).cpu()
+    for b in range(B):
+        assert (got[b, :lens[b]].double() - want[b][:lens[b]]).abs().max() < 1e-4
+        assert (got[b, lens[b]:] == 0).all()
+    for t in range(extra):
+        step = torch.stack([f[b, lens[b] + t] for b in range(B)])[:, None]
+        got = seqmix.retention_scan(*cut(step.to(device)), decay.to(device), state, slots, i32([1, 1, 1], device), False).cpu()
+        for b in range(B):
+            assert (got[b, 0].double() - want[b][lens[b] + t]).abs().max() < 1e-4, (b, t)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("H,G,D,V", [(4, 2, 20, 12), (2, 2, 64, 64), (3, 1, 9, 70), (1, 1, 130, 33)])
+def test_delta_rule_with_a_decay_per_key_channel(device, H, G, D, V):
+    g = torch.Generator().manual_seed(H * D + 1)
+    B, S, extra = 3, 19, 4
+    lens = [S, 1, 8]
+    T = S + extra
+    q, k, v = torch.randn(B, T, G, D, generator=g), torch.randn(B, T, G, D, generator=g), torch.randn(B, T, H, V, generator=g)
+    braw, araw = torch.randn(B, T, H, generator=g), torch.randn(B, T, H, D, generator=g) * 2
+    a_log, dt_bias = torch.randn(H, generator=g) * 0.5, torch.randn(H * D, generator=g)
+    want = []
+    for b in range(B):
+        n = lens[b] + extra
+        qq = q[b, :n].double() / torch.sqrt((q[b, :n].double() ** 2).sum(-1, keepdim=True) + 1e-6) * D ** -0.5
+        kk = k[b, :n].double() / torch.sqrt((k[b, :n].double() ** 2).sum(-1, keepdim=True) + 1e-6)
+        gg = torch.exp(-torch.exp(a_log.double())[None, :, None] * oracle.softplus(araw[b, :n].double() + dt_bias.double().view(H, D)))
+        o = torch.zeros(n, H, V, dtype=torch.float64)
+        for h in range(H):
+            M = torch.zeros(D, V, dtype=torch.float64)
+            for t in range(n):
+                M = gg[t, h][:, None] * M
+                u = oracle.sigmoid(braw[b, t, h].double()) * (v[b, t, h].double() - M.T @ kk[t, h // (H // G)])
+                M = M + torch.outer(kk[t, h // (H // G)], u)
+                o[t, h] = M.T @ qq[t, h // (H // G)]
+        want.append(o)
+    assert (gg.min() < 0.2) and (gg.max() > 0.8)                             # channels decay at very different rates
+    state = torch.full((5, H, D, V), float("nan"), device=device)
+    slots, dv = i32([3, 1, 0], device), (lambda t: t.to(device))
+    got = seqmix.gated_delta_scan(dv(q[:, :S]), dv(k[:, :S]), dv(v[:, :S]), dv(braw[:, :S]), dv(araw[:, :S]), dv(a_log), dv(dt_bias), state, slots,
+                                  i32(lens, device), True).cpu()
+    for b in range(B):
+        assert (got[b, :lens[b]].double() - want[b][:lens[b]]).abs().max() < 1e-4
+        assert (got[b, lens[b]:] == 0).all()
+    for t in range(extra):
+        pick = lambda a: dv(torch.stack([a[b, lens[b] + t] for b in range(B)])[:, None].contiguous())
+        got = seqmix.gated_delta_scan(pick(q), pick(k), pick(v), pick(braw), pick(araw), dv(a_log), dv(dt_bias), state, slots,
+                                      i32([1, 1, 1], device), False).cpu()
+        for b in range(B):
+            assert (got[b, 0].double() - want[b][lens[b] + t]).abs().max() < 1e-4, (b, t)
+
+
+def _headmix_expected(q, k, talk, coef, sink, gate, dims, base, chunk, window):
+    """One sequence, explicit sums: q [n,H,D], k [n,G,D] (values = k) → [n, H*D]."""
+    n, H, D = q.shape
+    G = k.shape[1]
+    qr, kr = oracle.rotate(q, dims, base, False), oracle.rotate(k, dims, base, False)
+    out = torch.zeros(n, H, D, dtype=torch.float64)
+    for i in range(n):
+        lo = 0
+        if chunk:
+            lo = (i // chunk) * chunk
+        if window:
+            lo = max(lo, i - window + 1)
+        raw = torch.stack([(kr[lo:i + 1, h // (H // G)] @ qr[i, h]) * coef[h] for h in range(H)])
+        sc = talk @ raw
+        for h in range(H):
+            top = max(float(sc[h].max()), float(sink[h]))
+            e = torch.exp(sc[h] - top)
+            out[i, h] = (e / (e.sum() + math.exp(float(sink[h]) - top))) @ k[lo:i + 1, h // (H // G)]
+    return out.reshape(n, H * D) * oracle.sigmoid(gate)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("H,G,D,chunk,window", [(4, 2, 16, 10, 0), (6, 3, 32, 0, 7), (4, 4, 24, 24, 0), (8, 2, 16, 32, 20), (2, 1, 48, 0, 0), (1, 1, 8, 1, 0)])
+def test_head_mixing_attention_prompt_and_ring(device, H, G, D, chunk, window):
+    """The attention ops alone: a batch of prompts of unequal lengths, then single tokens against the rings, across chunk borders."""
+    g = torch.Generator().manual_seed(H * D + chunk)
+    B, S, extra, dims, base = 3, 45, 30, D // 2, 300.0
+    lens = [45, 1, 20]
+    T = S + extra
+    q, k, gate = torch.randn(B, T, H, D, generator=g), torch.randn(B, T, G, D, generator=g), torch.randn(B, T, H * D, generator=g)
+    talk, coef, sink = torch.eye(H) + torch.randn(H, H, generator=g) * 0.4, (torch.randn(H, generator=g) * 0.2 + 1) / math.sqrt(D), torch.randn(H, generator=g)
+    want = [_headmix_expected(q[b, :lens[b] + extra].double(), k[b, :lens[b] + extra].double(), talk.double(), coef.double(), sink.double(),
+                              gate[b, :lens[b] + extra].double(), dims, base, chunk, window) for b in range(B)]
+    ring = min([s for s in (chunk, window) if s > 0] + [T])
+    kc, vc = torch.full((5, ring, G, D), float("nan"), device=device), torch.full((5, ring, G, D), float("nan"), device=device)
+    slots, dv = i32([4, 0, 2], device), (lambda t: t.to(device))
+    mixw, inv = dv(talk * coef[None, :]), seqmix.rotary_inv_freq(dims, base, device)
+    qm, rows = seqmix.headmix_qk_prepare(dv(q[:, :S]), dv(k[:, :S]), mixw, dims, inv, i32([0, 0, 0], device), i32(lens, device), slots, kc, vc, True)
+    out = torch.zeros(B * S, H * D + 8, device=device)
+    seqmix.headmix_attention_prompt(qm, rows, dv(k[:, :S]), dv(sink), dv(gate[:, :S]), i32(lens, device), chunk, window, out[:, 4:4 + H * D])
+    got = out[:, 4:4 + H * D].view(B, S, -1).cpu()
+    for b in range(B):
+        assert (got[b, :lens[b]].double() - want[b][:lens[b]]).abs().max() < 2e-5
+        assert (got[b, lens[b]:] == 0).all()
+    for t in range(extra):
+        pos = [n + t for n in lens]
+        pick = lambda a: dv(torch.stack([a[b, pos[b]] for b in range(B)])[:, None].contiguous())
+        qm, _ = seqmix.headmix_qk_prepare(pick(q), pick(k), mixw, dims, inv, i32(pos, device), i32([1, 1, 1], device), slots, kc, vc, False)
+        o1 = torch.zeros(B, H * D, device=device)
+        seqmix.headmix_attention_token(qm, kc, vc, dv(sink), pick(gate), slots, i32(pos, device), i32([1, 1, 1], device), chunk, window, o1)
+        for b in range(B):
+            assert (o1[b].cpu().double() - want[b][pos[b]]).abs().max() < 2e-5, (b, t)
+
+
+# ------------------------------------------------------------------------------------------------------------ one layer at a time
+SINGLE = {
+    "latent": [latent()],
+    "latent, one head, window 1": [latent(heads=1, dim=8, rot_dim=4, vdim=8, kv_rank=6, window=1)],
+    "latent lends to a wider window": [latent(window=4), retention(), latent(heads=2, dim=8, vdim=12, window=11, kv_from=0, mlp=None)],
+    "retention": [retention()],
+    "retention, all rotated, one head": [retention(heads=1, dim=8, vdim=5, dims=8, mlp=ffn(17, 0.7))],
+    "parallel": [par()],
+    "parallel, no groups, other taps": [par(left_spec(heads=2, kv_heads=2, dim=24, conv=4, chunk=5, dims=24), right_spec(heads=2, kv_heads=2, dim=8, vdim=8, conv=4))],
+    "parallel, one tap, one head": [par(left_spec(heads=1, kv_heads=1, dim=8, conv=1, chunk=30, dims=2), right_spec(heads=1, kv_heads=1, dim=5, vdim=33, conv=1), mlp=None)],
+}
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("name", sorted(SINGLE))
+def test_single_layer_models(device, name):
+    """Layers of each kind: the whole prompt at once, and one token followed by token-by-token decoding, against the oracle."""
+    cfg = make_cfg(SINGLE[name])
+    w = random_checkpoint(cfg, seed=len(name))
+    toks = tokens_for(cfg, 26, 5)
+    want = oracle.forward(cfg, w, toks)
+    model = build(cfg, w, device)
+    close(run_alone(model, toks, len(toks)), want, TOL32)
+    close(run_alone(model, toks, 1), want, TOL32)
+
+
+# ------------------------------------------------------------------------------------------------------------------ whole models
+MIXED = [latent(window=6), retention(), par(), latent(heads=2, dim=8, rot_dim=8, vdim=16, window=9, kv_from=0), retention(heads=2, dim=8, vdim=8, dims=4, mlp=ffn(24, 0.8)),
+         par(left_spec(heads=2, kv_heads=1, dim=8, conv=2, chunk=4, dims=8), right_spec(heads=2, kv_heads=1, dim=16, vdim=8, conv=3), mlp=None), latent(window=3)]
+
+
+@pytest.fixture(scope="module")
+def mixed():
+    cfg = make_cfg(MIXED)
+    w = random_checkpoint(cfg, seed=11)
+    toks = tokens_for(cfg, 48, 7)
+    stream = []
+    want = oracle.forward(cfg, w, toks, taps=stream)
+    return cfg, w, toks, want, stream
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("prompt", [48, 1, 2, 6, 31])
+def test_prompt_then_decode_matches_oracle(device, mixed, prompt):
+    cfg, w, toks, want, _ = mixed
+    close(run_alone(build(cfg, w, device), toks, prompt), want, TOL32)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_residual_stream_after_every_layer(device, mixed):
+    cfg, w, toks, _, stream = mixed
+    model = build(cfg, w, device)
+    seen = {}
+    model.forward_step(torch.tensor([toks], device=device), [len(toks)], [model.states.alloc()], [0], True, tap=lambda i, x: seen.__setitem__(i, x[0].cpu().clone()))
+    for i in range(len(MIXED)):
+        close(seen[i], stream[i], TOL32)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_unequal_batch_against_each_alone_and_reused_slots(device, mixed):
+    cfg, w, toks, _, _ = mixed
+    model = build(cfg, w, device)
+    reqs = [tokens_for(cfg, n, 20 + n) for n in (1 + 6, 7 + 6, 23 + 6, 2 + 6)]
+    prompts, steps = [1, 7, 23, 2], [0, 6, 3, 6]                      # row 0 ends with its prompt, row 2 leaves early
+    mgr = model.states
+    warm = [mgr.alloc() for _ in range(3)]                            # dirty a few slots first, then give them back
+    model.forward_step(torch.randint(0, 50, (3, 9), device=device), [9, 9, 9], warm, [0, 0, 0], True)
+    for s in warm:
+        mgr.free(s)
+    slots = [mgr.alloc() for _ in reqs]
+    assert set(warm) <= set(slots)
+    S = max(prompts)
+    ids = torch.zeros(len(reqs), S, dtype=torch.long)
+    for b, (r, p) in enumerate(zip(reqs, prompts)):
+        ids[b, :p] = torch.tensor(r[:p])
+    x = model.forward_step(ids.to(device), prompts, slots, [0] * len(reqs), True)
+    got = [[model.logits(x[b, :p]).cpu()] for b, p in enumerate(prompts)]
+    live = [b for b in range(len(reqs)) if steps[b] > 0]
+    mgr.free(slots[0])
+    for k in range(max(steps)):
+        live = [b for b in live if k < steps[b]]
+        step_ids = torch.tensor([[reqs[b][prompts[b] + k]] for b in live], device=device)
+        x = model.forward_step(step_ids, [1] * len(live), [slots[b] for b in live], [prompts[b] + k for b in live], False)
+        lg = model.logits(x[:, 0]).cpu()
+        for j, b in enumerate(live):
+            got[b].append(lg[j:j + 1])
+    for b, r in enumerate(reqs):
+        n = prompts[b] + steps[b]
+        close(torch.cat(got[b]), oracle.forward(cfg, w, r[:n]), TOL32)
+    fresh = build(cfg, w, device)
+    close(torch.cat(got[2]), run_alone(fresh, reqs[2][:26], 23), 1e-5)      # the batch changes nothing beyond rounding
+
+
+# ------------------------------------------------------------------------------------------ edges, the sink, far keys, long decoding
+def _needle_model(layers, vocab=40, width=48, seed=3):
+    """Token 0 is the needle: its embedding is large and unlike the others, so wherever a layer can still see it the logits move."""
+    cfg = make_cfg(layers, vocab=vocab, width=width)
+    w = random_checkpoint(cfg, seed=seed)
+    w["embed"][0] = (w["embed"][0] * 12).to(torch.bfloat16).float()
+    return cfg, w
+
+
+def _silence_right(w, layer):
+    """The recurrent branch of a parallel layer adds nothing: the only path to the past is the attention branch."""
+    w[f"l{layer}.mix.right.out"] = torch.zeros_like(w[f"l{layer}.mix.right.out"])
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("prompt", [40, 13, 1])
+def test_chunk_edges_with_a_needle(device, prompt):
+    """The needle sits at position 9 of a model whose only path to the past is attention inside chunks of 6 positions (the query and
+    key convolutions have one tap): the rest of its chunk, positions 9..11, sees it, position 12 on does not.  Checked in a prompt,
+    and with the chunk border passing over decoded tokens."""
+    chunk, at = 6, 9
+    cfg, w = _needle_model([par(left_spec(conv=1, chunk=chunk), right_spec(conv=1), mlp=None)])
+    _silence_right(w, 0)
+    toks = [1 + t % 7 for t in range(40)]
+    plain = list(toks)
+    toks[at] = 0
+    want, base = oracle.forward(cfg, w, toks), oracle.forward(cfg, w, plain)
+    moved = (want - base).abs().amax(-1)
+    assert (moved[at:12] > 1e-3).all() and (moved[12:] < 1e-9).all() and (moved[:at] < 1e-9).all()
+    close(run_alone(build(cfg, w, device), toks, prompt), want, TOL32)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("prompt", [40, 12, 1])
+def test_window_edges_with_a_needle_and_borrowed_latents(device, prompt):
+    """Latent attention only, no feed-forwards: layer 0 (window 6) and layer 1, which borrows layer 0's latents with window 4.  The
+    latents are made from layer 0's input, so the needle at position 9 is a key for 9..14 in layer 0 and for 9..12 in layer 1, and
+    nothing moves from position 15 on."""
+    at = 9
+    cfg, w = _needle_model([latent(window=6, mlp=None), latent(heads=2, dim=8, vdim=12, window=4, kv_from=0, mlp=None)])
+    toks = [1 + t % 7 for t in range(40)]
+    plain = list(toks)
+    toks[at] = 0
+    want, base = oracle.forward(cfg, w, toks), oracle.forward(cfg, w, plain)
+    moved = (want - base).abs().amax(-1)
+    assert (moved[at:at + 6] > 1e-3).all() and (moved[at + 6:] < 1e-9).all() and (moved[:at] < 1e-9).all()
+    close(run_alone(build(cfg, w, device), toks, prompt), want, TOL32)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_sink_takes_its_share_of_the_weights(device):
+    """Large sinks: most of every softmax's mass goes to the sink, so leaving it out (or scaling it) changes the logits visibly."""
+    cfg, w = _needle_model([par(mlp=None)], seed=8)
+    _silence_right(w, 0)
+    w["l0.mix.left.sink"] = torch.tensor([3.0, -1.0, 2.0, 4.0])
+    toks = tokens_for(cfg, 30, 2)
+    want = oracle.forward(cfg, w, toks)
+    off = dict(w)
+    off["l0.mix.left.sink"] = torch.full((4,), -60.0)
+    assert (oracle.forward(cfg, off, toks) - want).abs().max() > 1e-2
+    model = build(cfg, w, device)
+    close(run_alone(model, toks, 30), want, TOL32)
+    close(run_alone(model, toks, 4), want, TOL32)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("layer", ["retention", "delta"])
+def test_far_key_through_a_recurrent_state(device, layer):
+    """A needle 250 tokens back is still in the state: slow decays, a long prompt, then decoding; a lost or restarted state shows."""
+    if layer == "retention":
+        cfg, w = _needle_model([retention(heads=2, dim=16, vdim=16, decay=[0.999, 0.9995])], seed=5)
+    else:
+        cfg, w = _needle_model([par(left_spec(chunk=3), right_spec(heads=2, kv_heads=1, dim=16, vdim=16), mlp=None)], seed=5)
+        w["l0.mix.right.A_log"] = torch.full_like(w["l0.mix.right.A_log"], -7.0)       # decays close to 1: long memory
+        w["l0.mix.right.b"] = w["l0.mix.right.b"] * 0                                   # beta = 1/2 everywhere
+    toks = [1 + (t * 5) % 11 for t in range(280)]
+    plain = list(toks)
+    toks[4] = 0
+    want, base = oracle.forward(cfg, w, toks), oracle.forward(cfg, w, plain)
+    assert (want[-1] - base[-1]).abs().max() > 1e-3                         # the far token still matters at the end
+    model = build(cfg, w, device)
+    close(run_alone(model, toks, 250), want, TOL32)
+    close(run_alone(model, toks, 280), want, TOL32)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_long_decoding_from_one_token(device):
+    cfg = make_cfg([par(left_spec(chunk=16)), retention(), latent(window=40), latent(window=50, kv_from=2), par(left_spec(chunk=40, heads=2, kv_heads=2), mlp=None)])
+    w = random_checkpoint(cfg, seed=21)
+    toks = tokens_for(cfg, 130, 9)
+    close(run_alone(build(cfg, w, device), toks, 1), oracle.forward(cfg, w, toks), TOL32)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_chunk_and_window_larger_than_the_cache_limit(device):
+    """``max_seq_len`` below the chunk and the window: the rings are only as long as sequences can get."""
+    cfg = make_cfg([par(left_spec(chunk=500)), latent(window=400)])
+    w = random_checkpoint(cfg, seed=2)
+    toks = tokens_for(cfg, 30, 3)
+    model = build(cfg, w, device, max_seq_len=30)
+    assert model.states.layer(0)["left.k"].shape[1] == 30 and model.states.layer(1)["kv"].shape[1] == 30
+    close(run_alone(model, toks, 11), oracle.forward(cfg, w, toks), TOL32)
+
+
+def test_lender_keeps_the_widest_window_and_borrower_keeps_nothing(mixed):
+    cfg, w, _, _, _ = mixed
+    model = build(cfg, w, "cpu")
+    assert model.states.layer(0)["kv"].shape[1] == 9 and model.states.layer(3) == {}
+    with pytest.raises(ValueError):
+        build(make_cfg([latent(kv_from=1), latent()]), w, "cpu")
+
+
+def test_continuing_step_carries_one_token(mixed):
+    cfg, w, toks, _, _ = mixed
+    model = build(cfg, w, "cpu")
+    s = model.states.alloc()
+    model.forward_step(torch.tensor([toks[:4]]), [4], [s], [0], True)
+    with pytest.raises(ValueError):
+        model.forward_step(torch.tensor([toks[4:7]]), [3], [s], [4], False)
+
+
+# ---------------------------------------------------------------------------------------------- generation, registry, command lines
+def _oracle_greedy(cfg, w, prompt, n):
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(oracle.forward(cfg, w, toks)[-1].argmax()))
+    return toks[len(prompt):]
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_greedy_generation_through_the_serving_entry_points(device, mixed):
+    cfg, w, _, _, _ = mixed
+    prompts = [tokens_for(cfg, 9, 31), tokens_for(cfg, 4, 32)]
+    want = [_oracle_greedy(cfg, w, p, 5) for p in prompts]
+    model = build(cfg, w, device, batch_size=2)
+    model.on_device_sampling = True
+    ids = torch.zeros(2, 9, dtype=torch.long)
+    mask = torch.zeros(2, 9, dtype=torch.long)
+    for b, p in enumerate(prompts):
+        ids[b, :len(p)], mask[b, :len(p)] = torch.tensor(p), 1
+    out = model.generate(ids.to(device), 5, prompt_lens=mask.sum(1).to(device))
+    assert out.cpu().tolist() == want
+    out = HuggingFaceGenerationAdapter(model, pad_token_id=0).generate(ids.to(device), attention_mask=mask.to(device), max_new_tokens=5)
+    assert out[:, 9:].cpu().tolist() == want
+
+
+def _save_model_dir(path, cfg, w):
+    from neuronx_distributed_b200.utils.safetensors_utils import save_state_dict_safetensors
+
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    save_state_dict_safetensors({k: v.to(torch.bfloat16).contiguous() for k, v in w.items()}, os.path.join(path, "model.safetensors"))
+
+
+def _trace(cfg):
+    a, b, c = tokens_for(cfg, 14, 41), tokens_for(cfg, 5, 42), tokens_for(cfg, 9, 43)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:10], "want": [0, 9]}, {"id": "b", "tokens": b[:3], "want": [2]}], "end": []}]
+    for k in range(4):
+        ent = [{"id": "a", "tokens": [a[10 + k]], "want": [0]}]
+        if k < 2:
+            ent.append({"id": "b", "tokens": [b[3 + k]], "want": [] if k == 0 else [0]})
+        steps.append({"step": k + 1, "entries": ent, "end": (["b"] if k == 1 else []) + (["a"] if k == 3 else [])})
+    steps.append({"step": 5, "entries": [{"id": "c", "tokens": c, "want": [8]}], "end": ["c"]})
+    rows = {0: [("a", 0), ("a", 9), ("b", 2)], 1: [("a", 10)], 2: [("a", 11), ("b", 4)], 3: [("a", 12)], 4: [("a", 13)], 5: [("c", 8)]}
+    return {"a": a, "b": b, "c": c}, steps, rows
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_registry_checkpoint_reader_and_trace_replay(device, mixed, tmp_path):
+    import numpy as np
+
+    cfg, w, _, _, _ = mixed
+    _save_model_dir(str(tmp_path / "m"), cfg, w)
+    model = registry.load_for_serving(str(tmp_path / "m"), dtype=torch.float32, device=torch.device(device), max_seq_len=64, on_device_sampling=False)
+    assert isinstance(model, PulenexForInference)
+    reqs, steps, rows = _trace(cfg)
+    out = tmp_path / "o"
+    os.makedirs(out)
+    log = io.StringIO()
+    TraceReplayer(model, str(out)).run([json.dumps(s) for s in steps], log)
+    assert log.getvalue().split() == [x for s in steps for x in ("done", str(s["step"]))]
+    assert model.states.in_use == 0
+    for n, want_rows in rows.items():
+        got = torch.from_numpy(np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(len(want_rows), cfg["vocab"]).copy())
+        for j, (rid, pos) in enumerate(want_rows):
+            close(got[j:j + 1], oracle.forward(cfg, w, reqs[rid][:pos + 1])[-1:], TOL32)
+
+
+def test_trace_runner_command_line(mixed, tmp_path):
+    import numpy as np
+
+    cfg, w, _, _, _ = mixed
+    _save_model_dir(str(tmp_path / "m"), cfg, w)
+    reqs, steps, rows = _trace(cfg)
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", str(tmp_path / "m"), "--dtype", "float32", "--out", str(tmp_path / "o"),
+                        "--max-tokens", "40"], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    got = np.fromfile(tmp_path / "o" / "5.f32", dtype="<f4")
+    close(torch.from_numpy(got.copy())[None], oracle.forward(cfg, w, reqs["c"])[8:9], TOL32)
+
+
+def test_generate_command_line(mixed, tmp_path):
+    cfg, w, _, _, _ = mixed
+    _save_model_dir(str(tmp_path / "m"), cfg, w)
+    prompts = [tokens_for(cfg, 6, 51), tokens_for(cfg, 3, 52)]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    args = [os.path.join(ROOT, "bin", "generate"), "--model", str(tmp_path / "m"), "--dtype", "float32", "--max-new-tokens", "4"]
+    for p in prompts:
+        args += ["--prompt-ids", ",".join(map(str, p))]
+    r = subprocess.run(args, capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = [[int(t) for t in line.split(",")] for line in r.stdout.strip().splitlines()[-2:]]
+    assert got == [_oracle_greedy(cfg, w, p, 4) for p in prompts]
+
+
+# ---------------------------------------------------------------------------------------------------------------- bfloat16 (GPU)
+@pytest.mark.gpu
+def test_bfloat16_serving_close_to_the_oracle():
+    cfg = make_cfg([latent(heads=4, dim=16, rot_dim=16, vdim=16, kv_rank=32, window=9), retention(heads=2, dim=32, vdim=32, dims=16),
+                    par(left_spec(heads=4, kv_heads=2, dim=32, chunk=12, dims=16), right_spec(heads=2, kv_heads=1, dim=32, vdim=16)),
+                    latent(heads=4, dim=16, rot_dim=16, vdim=16, kv_rank=32, window=20, kv_from=0)], width=64)
+    w = random_checkpoint(cfg, seed=13)
+    toks = tokens_for(cfg, 40, 3)
+    want = oracle.forward(cfg, w, toks)
+    model = build(cfg, w, "cuda", dtype=torch.bfloat16)
+    close(run_alone(model, toks, 25), want, 5e-2)
+    close(run_alone(model, toks, 40), want, 5e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("H,G,D", [(4, 2, 16), (6, 2, 48), (2, 1, 128), (4, 4, 64), (8, 2, 128), (2, 2, 256)])
+@pytest.mark.parametrize("chunk,window", [(1, 0), (7, 0), (64, 0), (100, 30), (0, 33), (1000, 0)])
+def test_bfloat16_prompt_attention_in_one_kernel(H, G, D, chunk, window):
+    """The tensor-core prompt kernel against the same operands in double: chunk borders inside and across key tiles, windows,
+    unequal lengths, a sink and a gate."""
+    g = torch.Generator().manual_seed(H * D + chunk + window)
+    B, S = 2, 200
+    lens = [200, 77]
+    bf = lambda t: t.to(torch.bfloat16)
+    qm, k, gate = bf(torch.randn(B, S, H, G * D, generator=g) / math.sqrt(G * D)), bf(torch.randn(B, S, G, D, generator=g)), bf(torch.randn(B, S, H * D, generator=g))
+    v, sink = bf(torch.randn(B, S, G, D, generator=g)), torch.randn(H, generator=g)
+    out = torch.zeros(B * S, H * D, dtype=torch.bfloat16, device="cuda")
+    seqmix.headmix_attention_prompt(qm.cuda(), k.cuda(), v.cuda(), sink.cuda(), gate.cuda(), i32(lens, "cuda"), chunk, window, out)
+    got = out.view(B, S, H, D).cpu().double()
+    for b in range(B):
+        n = lens[b]
+        sc = torch.einsum("ihx,jx->hij", qm[b, :n].double(), k[b, :n].double().reshape(n, G * D))
+        i, j = torch.arange(n)[:, None], torch.arange(n)[None, :]
+        ok = j <= i
+        if chunk:
+            ok = ok & (i // chunk == j // chunk)
+        if window:
+            ok = ok & (i - j < window)
+        sc = torch.cat([sc.masked_fill(~ok, float("-inf")), sink.double().view(H, 1, 1).expand(H, n, 1)], -1)
+        p = torch.softmax(sc, -1)[..., :-1]
+        want = torch.einsum("hij,jhv->ihv", p, v[b, :n].double().repeat_interleave(H // G, 1)) * torch.sigmoid(gate[b, :n].double()).view(n, H, D)
+        assert (got[b, :n] - want).abs().max() < 3e-2
+        assert (got[b, n:] == 0).all()
