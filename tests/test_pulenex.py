@@ -236,8 +236,9 @@ def test_retention_scan_rows_of_many_lengths_and_a_carried_state(device, H, D, V
     B, extra = 3, 5
     lens = [S, 1, S // 2]
     f = torch.randn(B, S + extra, 2 * H * D + H * V, generator=g)
+    f[..., H * D:2 * H * D] *= 0.3                                          # q, k, v are views of one stacked tensor
     decay = torch.tensor([1.0 - 2.0 ** (-2 - 2 * h) for h in range(H)])
-    cut = lambda t: (t[..., :H * D].unflatten(-1, (H, D)), t[..., H * D:2 * H * D].unflatten(-1, (H, D)) * 0.3, t[..., 2 * H * D:].unflatten(-1, (H, V)))
+    cut = lambda t: (t[..., :H * D].unflatten(-1, (H, D)), t[..., H * D:2 * H * D].unflatten(-1, (H, D)), t[..., 2 * H * D:].unflatten(-1, (H, V)))
     want = []
     for b in range(B):
         n = lens[b] + extra
@@ -678,8 +679,11 @@ def test_bfloat16_serving_close_to_the_oracle():
     toks = tokens_for(cfg, 40, 3)
     want = oracle.forward(cfg, w, toks)
     model = build(cfg, w, "cuda", dtype=torch.bfloat16)
-    close(run_alone(model, toks, 25), want, 5e-2)
-    close(run_alone(model, toks, 40), want, 5e-2)
+    ref = (want - want.mean(-1, keepdim=True)).pow(2).mean().sqrt()
+    for prompt in (25, 40):                          # rounding noise of a small model with large weights: a few percent, no outliers
+        d = run_alone(model, toks, prompt).double() - want
+        err = (d - d.mean(-1, keepdim=True)).pow(2).mean(-1).sqrt() / ref
+        assert err.mean() < 4e-2 and err.max() < 0.2, (err.mean().item(), err.max().item())
 
 
 @pytest.mark.gpu
