@@ -291,8 +291,43 @@ __global__ void sigmoid_gate_mul_kernel(T* __restrict__ x, const TG* __restrict_
     stf(x + i, ldf(x + i) * sigmoidf_(ldf(gate + r * gate_stride + c / rep)));
 }
 
+// four consecutive coordinates per thread (C in whole fours); GV: the four have their own gates (rep == 1), else they share one
+template <typename T, typename TG, bool GV>
+__global__ void sigmoid_gate_mul_vec_kernel(T* __restrict__ x, const TG* __restrict__ gate, long gate_stride, long rows, int C, int rep) {
+    const long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= rows * C) return;
+    const long r = i / C;
+    const int c = (int)(i - r * C);
+    float4 v = ld4(x + i);
+    if (GV) {
+        const float4 g = ld4(gate + r * gate_stride + c);
+        v.x *= sigmoidf_(g.x); v.y *= sigmoidf_(g.y); v.z *= sigmoidf_(g.z); v.w *= sigmoidf_(g.w);
+    } else {
+        const float g = sigmoidf_(ldf(gate + r * gate_stride + c / rep));
+        v.x *= g; v.y *= g; v.z *= g; v.w *= g;
+    }
+    st4(x + i, v);
+}
+
 void sigmoid_gate_mul(void* x, int bf, const void* gate, int gate_bf, long gate_stride, long rows, int C, int rep, cudaStream_t s) {
     if (rows * C == 0) return;
+    const bool x_ok = C % 4 == 0 && (uintptr_t)x % 16 == 0;
+    const bool shared = x_ok && rep % 4 == 0;
+    const bool own = x_ok && rep == 1 && gate_stride % 4 == 0 && (uintptr_t)gate % 16 == 0;
+    if (shared || own) {
+        const unsigned blocks = (unsigned)((rows * C / 4 + 255) / 256);
+#define SEQMIX_SGM(T, TG)                                                                                                       \
+    do {                                                                                                                        \
+        if (own) sigmoid_gate_mul_vec_kernel<T, TG, true><<<blocks, 256, 0, s>>>((T*)x, (const TG*)gate, gate_stride, rows, C, rep);   \
+        else sigmoid_gate_mul_vec_kernel<T, TG, false><<<blocks, 256, 0, s>>>((T*)x, (const TG*)gate, gate_stride, rows, C, rep);      \
+    } while (0)
+        if (bf && gate_bf) SEQMIX_SGM(bf16, bf16);
+        else if (bf) SEQMIX_SGM(bf16, float);
+        else if (gate_bf) SEQMIX_SGM(float, bf16);
+        else SEQMIX_SGM(float, float);
+#undef SEQMIX_SGM
+        return;
+    }
     const unsigned blocks = (unsigned)((rows * C + 255) / 256);
     if (bf && gate_bf) sigmoid_gate_mul_kernel<bf16, bf16><<<blocks, 256, 0, s>>>((bf16*)x, (const bf16*)gate, gate_stride, rows, C, rep);
     else if (bf) sigmoid_gate_mul_kernel<bf16, float><<<blocks, 256, 0, s>>>((bf16*)x, (const float*)gate, gate_stride, rows, C, rep);

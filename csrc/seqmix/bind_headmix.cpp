@@ -73,6 +73,14 @@ void headmix_attention_token(const Tensor& qmix, const Tensor& kcache, const Ten
     const void* gp; long g_sb, g_st;
     gate_strides(gate, qmix, B, 1, H * D, gp, g_sb, g_st);
     if (sink) TORCH_CHECK(sink->numel() == H, "one sink per head");
+    if (seqmix::headmix_token_fits(is_bf(qmix), H, G, D, ring, qmix.data_ptr(), kcache.data_ptr(), vcache.data_ptr())) {
+        Tensor part = at::empty({B, seqmix::headmix_token_stretches(ring), H, D + 2}, qmix.options().dtype(at::kFloat));
+        seqmix::headmix_token(qmix.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), is_bf(qmix), sink ? f32(*sink) : nullptr, gp, g_sb,
+                              i32(slots), i32(pos0), i32(lens), (int)chunk, (int)window, ring, B, H, G, D, part.data_ptr<float>(),
+                              out.data_ptr(), out.stride(0), stream());
+        check_launch();
+        return;
+    }
     bool ok = seqmix::headmix_attend(qmix.data_ptr(), kcache.data_ptr(), (long)ring * G * D, vcache.data_ptr(), (long)ring * G * D, (long)G * D,
                                      is_bf(qmix), sink ? f32(*sink) : nullptr, gp, g_sb, g_st, i32(slots), i32(pos0), i32(lens), (int)chunk,
                                      (int)window, ring, B, 1, H, G, D, out.data_ptr(), out.stride(0), stream());

@@ -24,50 +24,70 @@ __global__ void __launch_bounds__(128) headmix_qk_prepare_kernel(
     int dims, const float* __restrict__ inv_freq, const int* __restrict__ pos0, const int* __restrict__ lens,
     const int* __restrict__ slots, T* __restrict__ kcache, T* __restrict__ vcache, int ring, T* __restrict__ qmix, T* __restrict__ rows,
     int S, int H, int G, int D) {
-    extern __shared__ float qs[];                 // [H][D] rotated queries
+    extern __shared__ __align__(16) float qs[];   // [H][D] rotated queries
     const int t = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
     const int len = min(lens[b], S);
     if (t >= len) return;                          // padding: nothing is read from these rows later
-    const int p = pos0[b] + t, half = dims / 2, per = D - half;      // units per head: `half` pairs, then the unrotated coordinates
+    const int p = pos0[b] + t, half = dims / 2, rest = D - dims;
     const T* qr = q + (long)b * q_sb + (long)t * q_st;
-    for (int u = tid; u < H * per; u += 128) {
-        const int h = u / per, i = u - h * per;
-        if (i < half) {
-            float a = ldf(qr + h * D + i), c = ldf(qr + h * D + i + half), sn, cs;
-            sincosf((float)p * inv_freq[i], &sn, &cs);
-            qs[h * D + i] = a * cs - c * sn;
-            qs[h * D + i + half] = c * cs + a * sn;
-        } else {
-            const int d = dims + (i - half);
-            qs[h * D + d] = ldf(qr + h * D + d);
-        }
-    }
     const T* kr = k + (long)b * k_sb + (long)t * k_st;
     const bool keep = t >= len - ring;             // the last `ring` tokens go to the rings
     const long crow = ((long)slots[b] * ring + (p % ring)) * G * D;
     T* rrow = rows ? rows + ((long)b * S + t) * G * D : nullptr;
-    for (int u = tid; u < G * per; u += 128) {
-        const int c = u / per, i = u - c * per;
-        if (i < half) {
-            const T ka = kr[c * D + i], kb = kr[c * D + i + half];
-            float a = ldf(&ka), cc = ldf(&kb), sn, cs;
+    // rotated pairs: the angle of pair i is the same for every query and key head, so sin / cos are formed once per pair and the
+    // thread walks the heads (the threads split into groups over the heads when the pairs are few)
+    if (half > 0) {
+        const int nh = H + G, groups = max(1, min(nh, 128 / half));
+        for (int u = tid; u < half * groups; u += 128) {
+            const int g = u / half, i = u - g * half;
+            float sn, cs;
             sincosf((float)p * inv_freq[i], &sn, &cs);
-            const float x = a * cs - cc * sn, y = cc * cs + a * sn;
-            if (rrow) { stf(rrow + c * D + i, x); stf(rrow + c * D + i + half, y); }
-            if (keep) {
-                stf(kcache + crow + c * D + i, x); stf(kcache + crow + c * D + i + half, y);
-                vcache[crow + c * D + i] = ka; vcache[crow + c * D + i + half] = kb;
+            for (int h = g; h < nh; h += groups) {
+                if (h < H) {
+                    const float a = ldf(qr + h * D + i), c = ldf(qr + h * D + i + half);
+                    qs[h * D + i] = a * cs - c * sn;
+                    qs[h * D + i + half] = c * cs + a * sn;
+                } else {
+                    const int c0 = (h - H) * D + i;
+                    const T ka = kr[c0], kb = kr[c0 + half];
+                    const float a = ldf(&ka), cc = ldf(&kb);
+                    const float x = a * cs - cc * sn, y = cc * cs + a * sn;
+                    if (rrow) { stf(rrow + c0, x); stf(rrow + c0 + half, y); }
+                    if (keep) {
+                        stf(kcache + crow + c0, x); stf(kcache + crow + c0 + half, y);
+                        vcache[crow + c0] = ka; vcache[crow + c0 + half] = kb;
+                    }
+                }
             }
-        } else {
-            const int d = dims + (i - half);
-            const T kv = kr[c * D + d];
-            if (rrow) rrow[c * D + d] = kv;
-            if (keep) { kcache[crow + c * D + d] = kv; vcache[crow + c * D + d] = kv; }
         }
+    }
+    for (int u = tid; u < H * rest; u += 128) {    // coordinates past the rotated ones pass unchanged
+        const int h = u / rest, d = h * D + dims + (u - h * rest);
+        qs[d] = ldf(qr + d);
+    }
+    for (int u = tid; u < G * rest; u += 128) {
+        const int c = u / rest, d = c * D + dims + (u - c * rest);
+        const T kv = kr[d];
+        if (rrow) rrow[d] = kv;
+        if (keep) { kcache[crow + d] = kv; vcache[crow + d] = kv; }
     }
     __syncthreads();
     const int hpg = H / G;
     T* qm = qmix + ((long)b * S + t) * H * G * D;
+    if (D % 4 == 0) {                              // four coordinates per thread
+        const int d4 = D / 4;
+        for (int o = tid; o < H * G * d4; o += 128) {
+            const int h = o / (G * d4), r = o - h * G * d4, c = r / d4, d = (r - c * d4) * 4;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int g = c * hpg; g < (c + 1) * hpg; ++g) {
+                const float m = mixw[h * H + g];
+                const float4 v = *reinterpret_cast<const float4*>(qs + g * D + d);
+                acc.x = fmaf(m, v.x, acc.x); acc.y = fmaf(m, v.y, acc.y); acc.z = fmaf(m, v.z, acc.z); acc.w = fmaf(m, v.w, acc.w);
+            }
+            st4(qm + ((long)h * G + c) * D + d, acc);
+        }
+        return;
+    }
     for (int o = tid; o < H * G * D; o += 128) {
         const int h = o / (G * D), r = o - h * G * D, c = r / D, d = r - c * D;
         float acc = 0.f;

@@ -109,6 +109,12 @@ void headmix_qk_prepare(const void* q, long q_sb, long q_st, const void* k, long
 bool headmix_attend(const void* qmix, const void* keys, long key_sb, const void* vals, long v_sb, long v_stride, int bf, const float* sink,
                     const void* gate, long g_sb, long g_st, const int* slots, const int* pos0, const int* lens, int chunk, int window,
                     int ring, int B, int S, int H, int G, int D, void* out, long out_stride, cudaStream_t s);
+// single tokens against the rings, all heads of a stretch of positions per block (headmix_decode.cu); part [B, stretches, H, D + 2] float
+int headmix_token_stretches(int ring);
+bool headmix_token_fits(int bf, int H, int G, int D, int ring, const void* qmix, const void* kcache, const void* vcache);
+void headmix_token(const void* qmix, const void* kcache, const void* vcache, int bf, const float* sink, const void* gate, long g_sb,
+                   const int* slots, const int* pos0, const int* lens, int chunk, int window, int ring, int B, int H, int G, int D,
+                   float* part, void* out, long out_stride, cudaStream_t s);
 bool headmix_prompt_mma_fits(const void* v, long v_sb, long v_st, int G, int D, const void* out, long out_stride);
 void headmix_prompt_mma(const void* qmix, const void* keys, const void* v, long v_sb, long v_st, const float* sink, const void* gate,
                         long g_sb, long g_st, const int* lens, int B, int S, int H, int G, int D, int chunk, int window, void* out,

@@ -35,7 +35,7 @@ GROUPS = {
                ["latent_kv_store", "rope_q_", "latent_window_attention", "window_softmax", "latent_prompt_attention",
                 "latent_prompt_attention_fits"]),
     "linrec": (["linear_recurrence.cu", "gla_chunked.cu", "bind_linrec.cpp"], ["gla_scan", "rglru_scan", "retention_scan"]),
-    "headmix": (["headmix_attention.cu", "headmix_prefill.cu", "bind_headmix.cpp"],
+    "headmix": (["headmix_attention.cu", "headmix_decode.cu", "headmix_prefill.cu", "bind_headmix.cpp"],
                 ["headmix_qk_prepare", "headmix_attention_prompt", "headmix_attention_token"]),
     "window": (["window_attention.cu", "window_prefill.cu", "bind_window.cpp"], ["window_qk_prepare", "window_attention_prompt", "window_attention_token"]),
     "matrec": (["matrix_recurrence.cu", "bind_matrec.cpp"], ["gated_delta_scan", "ssd_scan"]),

@@ -358,6 +358,54 @@ def test_head_mixing_attention_prompt_and_ring(device, H, G, D, chunk, window):
             assert (o1[b].cpu().double() - want[b][pos[b]]).abs().max() < 2e-5, (b, t)
 
 
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,D,chunk,window,ring", [(4, 2, 16, 100, 0, 100), (16, 4, 32, 0, 70, 70), (3, 1, 9, 50, 0, 50), (2, 2, 136, 90, 33, 40),
+                                                      (8, 1, 24, 0, 0, 150), (6, 6, 160, 64, 0, 64), (5, 5, 260, 40, 0, 40)])
+def test_single_tokens_against_long_rings(device, dtype, H, G, D, chunk, window, ring):
+    """Single tokens whose visible stretch spans several blocks of ring rows and wraps around the ring's end, rows at different
+    positions (a chunk's first and last token, just past a wrap), a row without a token, rows the sequence never wrote holding NaN;
+    key rows of 9 to 1300 numbers, also sizes that are not whole fours."""
+    if device == "cpu" and dtype == torch.bfloat16:
+        pytest.skip("the plain statements are covered in float")
+    g = torch.Generator().manual_seed(H * D + chunk + ring)
+    DK = G * D
+    pos = [ring * 3 + 5, max(chunk, 1) * 2, max(chunk, 1) * 2 - 1, 0, 7] if chunk or window else [ring - 1, 40, 33, 0, 7]   # no mask: the ring holds all
+    lens = [1, 1, 1, 1, 0]
+    B, slots = len(pos), [6, 1, 3, 0, 2]
+    cast = lambda t: t.to(dtype).to(device)
+    qm, gate, sink = torch.randn(B, 1, H, DK, generator=g) / math.sqrt(DK), torch.randn(B, 1, H * D, generator=g), torch.randn(H, generator=g)
+    kc, vc = torch.full((7, ring, G, D), float("nan")), torch.full((7, ring, G, D), float("nan"))
+    spans = []
+    for b in range(B):
+        i, lo = pos[b], 0
+        if chunk:
+            lo = (i // chunk) * chunk
+        if window:
+            lo = max(lo, i - window + 1)
+        spans.append((lo, i))
+        for j in range(lo, i + 1):
+            kc[slots[b], j % ring], vc[slots[b], j % ring] = torch.randn(G, D, generator=g), torch.randn(G, D, generator=g)
+    kc, vc, qm, gate = kc.to(dtype), vc.to(dtype), qm.to(dtype), gate.to(dtype)
+    out = torch.full((B, H * D + 4), 7.0, dtype=dtype, device=device)
+    seqmix.headmix_attention_token(qm.to(device), kc.to(device), vc.to(device), sink.to(device), gate.to(device), i32(slots, device), i32(pos, device),
+                                   i32(lens, device), chunk, window, out[:, :H * D])
+    got = out.cpu().double()
+    assert (got[:, H * D:] == 7.0).all()
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    for b in range(B):
+        if lens[b] == 0:
+            assert (got[b, :H * D] == 0).all()
+            continue
+        lo, i = spans[b]
+        rows = [j % ring for j in range(lo, i + 1)]
+        K, V = kc[slots[b], rows].double().reshape(len(rows), DK), vc[slots[b], rows].double()
+        sc = torch.cat([qm[b, 0].double() @ K.T, sink.double()[:, None]], 1)
+        p = torch.softmax(sc, -1)[:, :-1]
+        want = torch.einsum("hj,jhv->hv", p, V.repeat_interleave(H // G, 1)).reshape(H * D) * torch.sigmoid(gate[b, 0].double())
+        assert (got[b, :H * D] - want).abs().max() < tol, (b, (got[b, :H * D] - want).abs().max())
+
+
 # ------------------------------------------------------------------------------------------------------------ one layer at a time
 SINGLE = {
     "latent": [latent()],
