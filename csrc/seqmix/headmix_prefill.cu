@@ -208,14 +208,18 @@ static size_t headmix_prompt_smem(int DK, int D, int KT) {
 bool headmix_prompt_mma_fits(const void* v, long v_sb, long v_st, int G, int D, const void* out, long out_stride) {
     auto a16 = [](const void* p) { return (uintptr_t)p % 16 == 0; };
     return D % 16 == 0 && D <= 256 && a16(v) && v_sb % 8 == 0 && v_st % 8 == 0 && (uintptr_t)out % 4 == 0 && out_stride % 2 == 0 &&
-           headmix_prompt_smem(G * D, D, 32) <= 200 * 1024;
+           headmix_prompt_smem(G * D, D, 16) <= 200 * 1024;
 }
 
 void headmix_prompt_mma(const void* qmix, const void* keys, const void* v, long v_sb, long v_st, const float* sink, const void* gate,
                         long g_sb, long g_st, const int* lens, int B, int S, int H, int G, int D, int chunk, int window, void* out,
                         long out_stride, cudaStream_t s) {
-    const bool wide = headmix_prompt_smem(G * D, D, 64) <= 200 * 1024;
-    const size_t smem = headmix_prompt_smem(G * D, D, wide ? 64 : 32);
+    // keys per tile: the most that leaves room for two blocks per SM (each block has only four warps, and a second block hides the
+    // first one's waits on its staged tiles); if none does, the most that fits at all
+    int kt = 0;
+    for (int c : {64, 32, 16}) if (!kt && headmix_prompt_smem(G * D, D, c) <= 112 * 1024) kt = c;
+    for (int c : {64, 32, 16}) if (!kt && headmix_prompt_smem(G * D, D, c) <= 200 * 1024) kt = c;
+    const size_t smem = headmix_prompt_smem(G * D, D, kt);
     dim3 grid((S + kHQ - 1) / kHQ, H, B);
 #define SEQMIX_HPM(KT, Bv)                                                                                                            \
     do {                                                                                                                              \
@@ -225,7 +229,7 @@ void headmix_prompt_mma(const void* qmix, const void* keys, const void* v, long 
                                                                   (bf16*)out, out_stride);                                            \
     } while (0)
 #define SEQMIX_HPM_V(KT) do { if (D <= 64) SEQMIX_HPM(KT, 4); else if (D <= 128) SEQMIX_HPM(KT, 8); else SEQMIX_HPM(KT, 16); } while (0)
-    if (wide) SEQMIX_HPM_V(64); else SEQMIX_HPM_V(32);
+    if (kt == 64) SEQMIX_HPM_V(64); else if (kt == 32) SEQMIX_HPM_V(32); else SEQMIX_HPM_V(16);
 #undef SEQMIX_HPM_V
 #undef SEQMIX_HPM
 }
