@@ -1,13 +1,14 @@
 // Elementwise activations and the small-batch pieces of a routed feed-forward.
 //   xielu        : z > 0: ap z^2 + z/2;  z <= 0: an (exp(z) - 1 - z) + z/2   (ap, an are positive numbers prepared by the caller)
 //   gelu_erf     : 0.5 z (1 + erf(z / sqrt 2))
+//   relu_sq      : max(z, 0)^2
 //   silu_mul     : silu(gate) * up for rows [gate | up]
 //   clamped_glu  : g = min(gate, limit), u = clamp(up, -limit, limit), g sigmoid(slope g) (u + 1) for rows [gate | up]
 //   sigmoid_gate_mul : x *= sigmoid(gate), one gate number per `rep` consecutive coordinates (a head, or one coordinate)
 //   indexed_gemv : out[m,:] = act(W[sel[m]] x[m,:]) for a few rows m, each with its own matrix out of a stack [E, O, I]
 //                  (token generation: the chosen experts' matrices are streamed once, a warp per output row); act 0: none,
 //                  1: gelu_erf, 2: the matrix stacks gate rows over up rows and out = silu(gate row . x) * (up row . x), O/2 columns;
-//                  rows whose sel names no matrix give zeros
+//                  3: the square of relu; rows whose sel names no matrix give zeros
 //   moe_combine  : y[n,:] = base_weight[n] * base[n,:] + sum_k weight[n,k] * rows[src[n,k],:], summed in float
 //   route_topk   : scores, choice with a correction, top-k, weights and the identity experts' share in one launch
 //   small_linear_f32 : a few rows times a matrix with float results (router logits, per-head scalars of the recurrences)
@@ -22,6 +23,13 @@ __device__ __forceinline__ float xielu_(float z, float ap, float an) {
     return z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
 }
 
+__device__ __forceinline__ float relu_sq_(float z) { const float r = fmaxf(z, 0.f); return r * r; }
+
+template <int ACT>
+__device__ __forceinline__ float act_value(float z, float ap, float an) {
+    return ACT == 0 ? xielu_(z, ap, an) : (ACT == 1 ? gelu_erf_(z) : relu_sq_(z));
+}
+
 // 16 bytes per thread and access (8 bfloat16 / 4 float); `n16` counts whole 16-byte groups, the tail goes one by one
 template <typename T, int ACT>
 __global__ void act_kernel(const T* __restrict__ x, T* __restrict__ out, long n, long n16, float ap, float an) {
@@ -33,12 +41,12 @@ __global__ void act_kernel(const T* __restrict__ x, T* __restrict__ out, long n,
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
             const float z = ldf(e + k);
-            stf(e + k, ACT == 0 ? xielu_(z, ap, an) : gelu_erf_(z));
+            stf(e + k, act_value<ACT>(z, ap, an));
         }
         reinterpret_cast<uint4*>(out)[i] = raw;
     } else {
         const long j = n16 * VEC + (i - n16);
-        if (j < n) { const float z = ldf(x + j); stf(out + j, ACT == 0 ? xielu_(z, ap, an) : gelu_erf_(z)); }
+        if (j < n) stf(out + j, act_value<ACT>(ldf(x + j), ap, an));
     }
 }
 
@@ -87,6 +95,7 @@ __global__ void indexed_gemv_kernel(const T* __restrict__ w, const int* __restri
     const T* xr = x + (long)m * x_stride;
     float acc = row_dot<T, VEC>(wr, xr, I, lane);
     if (act == 1) acc = gelu_erf_(acc);
+    else if (act == 3) acc = relu_sq_(acc);
     else if (act == 2) acc = acc * sigmoidf_(acc) * row_dot<T, VEC>(wr + (long)On * I, xr, I, lane);
     if (lane == 0) stf(out + (long)m * On + o, acc);
 }
@@ -114,7 +123,8 @@ __global__ void moe_combine_kernel(const T* __restrict__ rows, const int* __rest
 
 // Router: a warp per row.  scores = softmax (kind 1) or sigmoid (kind 0) of the row's logits; the `top` largest of scores + correction
 // are chosen (ties: the lower index), in descending order; a chosen real expert (index < n_real) gets weight score * scale, a chosen
-// identity expert weight 0 while its score is added to ident[row].  PL: logits per lane (E <= 32 PL).
+// identity expert weight 0 while its score is added to ident[row].  Kind 2: the scores are the logits themselves and the weights
+// are the softmax over the CHOSEN logits only (times scale).  PL: logits per lane (E <= 32 PL).
 template <int PL>
 __global__ void route_topk_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int N, int E, int top, int n_real,
                                   int kind, float scale, float* __restrict__ w, long* __restrict__ idx, float* __restrict__ ident) {
@@ -138,7 +148,7 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, const float*
         sum = warp_sum(sum);
 #pragma unroll
         for (int i = 0; i < PL; ++i) sc[i] = sc[i] / sum;
-    } else {
+    } else if (kind == 0) {
 #pragma unroll
         for (int i = 0; i < PL; ++i) sc[i] = lane + 32 * i < E ? sigmoidf_(sc[i]) : 0.f;
     }
@@ -147,7 +157,7 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, const float*
         const int e = lane + 32 * i;
         ch[i] = e < E ? sc[i] + (correction ? correction[e] : 0.f) : -INFINITY;
     }
-    float idw = 0.f;
+    float idw = 0.f, first = 0.f, total = 0.f, keep = 0.f;
     for (int t = 0; t < top; ++t) {
         float bv = -INFINITY, bs = 0.f;
         int be = 0x7fffffff;
@@ -168,11 +178,25 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, const float*
             for (int i = 0; i < PL; ++i)
                 if (lane + 32 * i == e) ch[i] = -INFINITY;
         }
+        if (kind == 2) {                                                         // every lane follows the sum; lane t keeps the t-th
+            if (t == 0) first = s_e;                                             // exponential (the first chosen logit is the largest)
+            const float x = expf(s_e - first);
+            total += x;
+            if (t == lane) keep = x;
+            if (t >= 32 && lane == 0) w[(long)row * top + t] = x;                // beyond a warp's worth: through memory
+        }
         if (lane == 0) {
             idx[(long)row * top + t] = e;
-            w[(long)row * top + t] = e < n_real ? s_e * scale : 0.f;
-            if (e >= n_real) idw += s_e;
+            if (kind != 2) {
+                w[(long)row * top + t] = e < n_real ? s_e * scale : 0.f;
+                if (e >= n_real) idw += s_e;
+            }
         }
+    }
+    if (kind == 2) {
+        if (lane < top) w[(long)row * top + lane] = keep / total * scale;
+        if (top > 32 && lane == 0)
+            for (int t = 32; t < top; ++t) w[(long)row * top + t] = w[(long)row * top + t] / total * scale;
     }
     if (lane == 0 && ident) ident[row] = idw;
 }
@@ -220,6 +244,11 @@ void xielu(const void* x, void* out, int bf, long n, float ap, float an, cudaStr
 void gelu_erf(const void* x, void* out, int bf, long n, cudaStream_t s) {
     if (n == 0) return;
     if (bf) act_launch<bf16, 1>(x, out, n, 0.f, 0.f, s); else act_launch<float, 1>(x, out, n, 0.f, 0.f, s);
+}
+
+void relu_sq(const void* x, void* out, int bf, long n, cudaStream_t s) {
+    if (n == 0) return;
+    if (bf) act_launch<bf16, 2>(x, out, n, 0.f, 0.f, s); else act_launch<float, 2>(x, out, n, 0.f, 0.f, s);
 }
 
 template <typename T>

@@ -65,11 +65,19 @@ Tensor gelu_erf(const Tensor& x) {
     return out;
 }
 
+Tensor relu_sq(const Tensor& x) {
+    TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "x must be contiguous");
+    Tensor out = at::empty_like(x);
+    seqmix::relu_sq(x.data_ptr(), out.data_ptr(), is_bf(x), x.numel(), stream());
+    check_launch();
+    return out;
+}
+
 // w [E,O,I], sel int [M], x [M,I] → act(w[sel[m]] x[m]): [M,O], or [M,O/2] for the gated kind (act 2)
 Tensor indexed_gemv(const Tensor& w, const Tensor& sel, const Tensor& x, int64_t act) {
     TORCH_CHECK(w.is_cuda() && w.dim() == 3 && w.is_contiguous() && x.dim() == 2 && x.stride(1) == 1 && x.scalar_type() == w.scalar_type(), "bad gemv operands");
     const int M = x.size(0), E = w.size(0), O = w.size(1), I = w.size(2);
-    TORCH_CHECK(x.size(1) == I && sel.numel() == M && act >= 0 && act <= 2 && (act != 2 || O % 2 == 0), "shape mismatch");
+    TORCH_CHECK(x.size(1) == I && sel.numel() == M && act >= 0 && act <= 3 && (act != 2 || O % 2 == 0), "shape mismatch");
     Tensor out = at::empty({M, act == 2 ? O / 2 : O}, x.options());
     seqmix::indexed_gemv(w.data_ptr(), i32(sel), x.data_ptr(), is_bf(x), x.stride(0), M, E, O, I, (int)act, out.data_ptr(), stream());
     check_launch();
@@ -110,6 +118,48 @@ Tensor embed_sinusoid(const Tensor& tokens, const Tensor& table, double scale, c
                            (int)table.size(0), out.data_ptr<float>(), stream());
     check_launch();
     return out;
+}
+
+// tokens int64 [B,S], table [vocab, W], pairs [buckets + 1, W] (optional), prev int64 [slots] (optional) → float [B,S,W] (+ a copy in
+// the table's dtype when `want_lp`)
+std::vector<Tensor> embed_bigram(const Tensor& tokens, const Tensor& table, double scale, const c10::optional<Tensor>& pairs, int64_t mul_prev,
+                                 int64_t mul_cur, const c10::optional<Tensor>& prev, const Tensor& slots, const Tensor& lens, bool fresh,
+                                 bool want_lp) {
+    TORCH_CHECK(tokens.is_cuda() && tokens.dim() == 2 && tokens.is_contiguous() && tokens.scalar_type() == at::kLong && table.dim() == 2 &&
+                    table.is_contiguous(), "tokens must be contiguous int64 [B,S], table [vocab, W]");
+    const int B = tokens.size(0), S = tokens.size(1), W = table.size(1);
+    long buckets = 0;
+    if (pairs) {
+        TORCH_CHECK(pairs->dim() == 2 && pairs->is_contiguous() && pairs->size(1) == W && pairs->size(0) >= 2 &&
+                        pairs->scalar_type() == table.scalar_type(), "pairs must be [buckets + 1, W] of the table's dtype");
+        buckets = pairs->size(0) - 1;
+    }
+    if (prev) TORCH_CHECK(prev->is_cuda() && prev->scalar_type() == at::kLong && prev->is_contiguous(), "prev must be int64 [slots]");
+    TORCH_CHECK(slots.numel() == B && lens.numel() == B, "one slot and one length per row");
+    Tensor out = at::empty({B, S, W}, table.options().dtype(at::kFloat));
+    Tensor lp = want_lp ? at::empty({B, S, W}, table.options()) : Tensor();
+    seqmix::embed_bigram(tokens.data_ptr<int64_t>(), table.data_ptr(), is_bf(table), (float)scale, pairs ? pairs->data_ptr() : nullptr, buckets,
+                         mul_prev, mul_cur, prev ? (long*)prev->data_ptr<int64_t>() : nullptr, i32(slots), i32(lens), fresh, B, S, W,
+                         (int)table.size(0), out.data_ptr<float>(), want_lp ? lp.data_ptr() : nullptr, stream());
+    check_launch();
+    return {out, lp};
+}
+
+// x float [rows, C] (in place) <- norm(alpha x + sigmoid(gate) y) * w; y, gate [rows, C] views of one dtype; lp: a copy in that dtype
+void postnorm_gated_(Tensor x, const Tensor& y, const c10::optional<Tensor>& gate, const Tensor& w, double alpha, double eps,
+                     const c10::optional<Tensor>& lp) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1 && x.scalar_type() == at::kFloat && y.dim() == 2 && y.stride(1) == 1,
+                "x must be float [rows, C], y [rows, C]");
+    const int rows = x.size(0), C = x.size(1);
+    TORCH_CHECK(y.size(0) == rows && y.size(1) == C && w.numel() == C, "shape mismatch");
+    if (gate) TORCH_CHECK(gate->dim() == 2 && gate->stride(1) == 1 && gate->size(0) == rows && gate->size(1) == C &&
+                              gate->scalar_type() == y.scalar_type(), "gate must be [rows, C] of y's dtype");
+    if (lp) TORCH_CHECK(lp->dim() == 2 && lp->stride(1) == 1 && lp->size(0) == rows && lp->size(1) == C && lp->scalar_type() == y.scalar_type(),
+                        "the copy must be [rows, C] of y's dtype");
+    seqmix::postnorm_gated(x.data_ptr<float>(), x.stride(0), y.data_ptr(), y.stride(0), gate ? gate->data_ptr() : nullptr,
+                           gate ? gate->stride(0) : 0, is_bf(y), f32(w), (float)alpha, (float)eps, rows, C, lp ? lp->data_ptr() : nullptr,
+                           lp ? lp->stride(0) : 0, stream());
+    check_launch();
 }
 
 // x [rows, C], gate [rows, C] (row strides free), w float [C] or [C / groups] → out [rows, C] (row stride free) of the gate's dtype
@@ -192,6 +242,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("add_rms_norm_", &add_rms_norm_);
     m.def("xielu", &xielu);
     m.def("gelu_erf", &gelu_erf);
+    m.def("relu_sq", &relu_sq);
+    m.def("embed_bigram", &embed_bigram);
+    m.def("postnorm_gated_", &postnorm_gated_);
     m.def("silu_mul", &silu_mul);
     m.def("indexed_gemv", &indexed_gemv);
     m.def("moe_combine", &moe_combine);

@@ -2,6 +2,8 @@
 // (with `center`, x's mean is taken off first: a layer norm with a gain and no bias, two passes over the row for the statistics),
 // optionally times silu(gate), written out or accumulated into a float residual stream (x_res += norm(y): the residual sum of a
 // layer that normalises the sublayer's OUTPUT).  Statistics in float.
+//   postnorm_gated: the closing step of a block whose norm comes AFTER the residual sum, x <- norm(alpha * x + sigmoid(gate) * y) * w,
+//   on a float stream in place (gate optional), with an optional copy of the result in the sublayers' dtype.
 #include "seq_common.cuh"
 #include "seqmix.h"
 
@@ -139,6 +141,105 @@ __global__ void group_rms_norm_gated_kernel(const Tin* __restrict__ x, long x_st
         const float z = ldf(gr + c);
         stf(o + c, ldf(xr + c) * gf(z) * inv * wr[c]);
     }
+}
+
+// blockDim.x threads share a row (32: a warp per row, narrow rows; 256: a block per row, rows from 1024 coordinates on and single-token
+// steps), blockDim.y rows per block; a thread meets the same coordinates in both passes, so the stream is updated in place.  VEC:
+// four consecutive coordinates per thread and access.  NIT > 0 (VEC only): the row has at most NIT * 4 * blockDim.x coordinates and
+// a thread keeps its mixed values in registers between the statistics and the scaling, so the stream, the sublayer's result and
+// the gate are read once (rows up to 4096 coordinates with a block per row; beyond that the two-pass form).
+template <typename T, bool VEC, int NIT>
+__global__ void postnorm_gated_kernel(float* x, long x_stride, const T* __restrict__ y, long y_stride, const T* __restrict__ gate,
+                                      long gate_stride, const float* __restrict__ w, float alpha, float eps, int rows, int C,
+                                      T* __restrict__ lp, long lp_stride) {
+    __shared__ float part[8];
+    const int row = blockIdx.x * blockDim.y + threadIdx.y, tx = threadIdx.x, TX = blockDim.x;
+    const bool on = row < rows;
+    float* xr = x + (long)(on ? row : 0) * x_stride;
+    const T* yr = y + (long)(on ? row : 0) * y_stride;
+    const T* gr = gate ? gate + (long)(on ? row : 0) * gate_stride : nullptr;
+    auto mix1 = [&](float xv, float yv, float gv) { return fmaf(alpha, xv, gr ? sigmoidf_(gv) * yv : yv); };
+    auto mix4 = [&](int c) {
+        const float4 a = ld4(xr + c), b = ld4(yr + c), g = gr ? ld4(gr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        return make_float4(mix1(a.x, b.x, g.x), mix1(a.y, b.y, g.y), mix1(a.z, b.z, g.z), mix1(a.w, b.w, g.w));
+    };
+    float4 kept[NIT > 0 ? NIT : 1];
+    float ss = 0.f;
+    if (on) {
+        if (NIT > 0) {
+#pragma unroll
+            for (int i = 0; i < NIT; ++i) {
+                const int c = (i * TX + tx) * 4;
+                if (c < C) {
+                    kept[i] = mix4(c);
+                    ss = fmaf(kept[i].x, kept[i].x, fmaf(kept[i].y, kept[i].y, fmaf(kept[i].z, kept[i].z, fmaf(kept[i].w, kept[i].w, ss))));
+                }
+            }
+        } else if (VEC) {
+            for (int c = tx * 4; c < C; c += TX * 4) {
+                const float4 v = mix4(c);
+                ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+            }
+        } else {
+            for (int c = tx; c < C; c += TX) { const float v = mix1(xr[c], ldf(yr + c), gr ? ldf(gr + c) : 0.f); ss = fmaf(v, v, ss); }
+        }
+    }
+    ss = warp_sum(ss);
+    if (TX > 32) {                              // one row per block: fold the warps' sums
+        if ((tx & 31) == 0) part[tx >> 5] = ss;
+        __syncthreads();
+        ss = 0.f;
+        for (int k = 0; k < TX / 32; ++k) ss += part[k];
+    }
+    if (!on) return;
+    const float inv = 1.f / sqrtf(ss / (float)C + eps);
+    auto put4 = [&](int c, float4 m) {
+        const float4 u = ld4(w + c);
+        const float4 v = make_float4(m.x * inv * u.x, m.y * inv * u.y, m.z * inv * u.z, m.w * inv * u.w);
+        st4(xr + c, v);
+        if (lp) st4(lp + (long)row * lp_stride + c, v);
+    };
+    if (NIT > 0) {
+#pragma unroll
+        for (int i = 0; i < NIT; ++i) {
+            const int c = (i * TX + tx) * 4;
+            if (c < C) put4(c, kept[i]);
+        }
+        return;
+    }
+    if (VEC) {
+        for (int c = tx * 4; c < C; c += TX * 4) put4(c, mix4(c));
+        return;
+    }
+    for (int c = tx; c < C; c += TX) {
+        const float v = mix1(xr[c], ldf(yr + c), gr ? ldf(gr + c) : 0.f) * inv * w[c];
+        xr[c] = v;
+        if (lp) stf(lp + (long)row * lp_stride + c, v);
+    }
+}
+
+void postnorm_gated(float* x, long x_stride, const void* y, long y_stride, const void* gate, long gate_stride, int bf, const float* w,
+                    float alpha, float eps, int rows, int C, void* lp, long lp_stride, cudaStream_t s) {
+    if (rows == 0) return;
+    const bool few = C >= 1024 || (rows < 148 * 8 && C >= 512);      // a block per row: wide rows stay in registers that way
+    dim3 block(few ? 256 : 32, few ? 1 : 8), grid(few ? rows : (rows + 7) / 8);
+    const size_t e = bf ? 2 : 4;
+    auto al = [](const void* p, size_t b) { return p == nullptr || (uintptr_t)p % b == 0; };
+    const bool vec = C % 4 == 0 && x_stride % 4 == 0 && y_stride % 4 == 0 && (!gate || gate_stride % 4 == 0) && (!lp || lp_stride % 4 == 0) &&
+                     al(x, 16) && al(w, 16) && al(y, 4 * e) && al(gate, 4 * e) && al(lp, 4 * e);
+    const int per = vec ? (C / 4 + (int)block.x - 1) / (int)block.x : 0;   // 16-byte groups per thread
+#define SEQMIX_PN(T, V, N)                                                                                                           \
+    postnorm_gated_kernel<T, V, N><<<grid, block, 0, s>>>(x, x_stride, (const T*)y, y_stride, (const T*)gate, gate_stride, w, alpha, eps,   \
+                                                          rows, C, (T*)lp, lp_stride)
+#define SEQMIX_PN_T(T)                                                                                                               \
+    do {                                                                                                                             \
+        if (!vec) SEQMIX_PN(T, false, 0);                                                                                            \
+        else if (per <= 4) SEQMIX_PN(T, true, 4);                                                                                    \
+        else SEQMIX_PN(T, true, 0);                                                                                                  \
+    } while (0)
+    if (bf) SEQMIX_PN_T(bf16); else SEQMIX_PN_T(float);
+#undef SEQMIX_PN_T
+#undef SEQMIX_PN
 }
 
 void group_rms_norm_gated(const void* x, int in_bf16, long x_stride, const void* gate, int gate_bf16, long gate_stride, const float* w,

@@ -4,7 +4,11 @@
 ``W_down gelu(W_up h)`` with ``up [E, ff, width]``, or gated, ``W_down (silu(W_gate h) * (W_up h))`` with the gate rows stacked
 over the up rows in ``up [E, 2 ff, width]``; ``down [E, width, ff]``.
 
-Two options of the router.  ``choice_bias``: a float vector added to the scores for the CHOICE only (the weights stay the plain
+``router_act="softmax_top"``: the ``top`` largest LOGITS are chosen and the weights are the softmax over the chosen logits only
+(renormalised by construction).  ``router_bias``: the logits are ``W_router h + b``.  ``expert_act``: the plain experts' activation,
+``"gelu"`` (erf form) or ``"relu_sq"`` (the square of relu).
+
+Two more options of the router.  ``choice_bias``: a float vector added to the scores for the CHOICE only (the weights stay the plain
 scores).  ``identity_experts``: the router's last outputs name experts without tensors whose output is the input itself; their
 weights are summed per token and enter the combine as a weighted copy of the input.
 
@@ -31,11 +35,17 @@ class RoutedFFN(nn.Module):
 
     def __init__(self, width: int, ff: int, experts: int, top: int, weight_scale: float = 1.0, shared_ff: int = 0,
                  router_act: str = "sigmoid", gated: bool = False, identity_experts: int = 0, choice_bias: bool = False,
-                 dtype: torch.dtype = torch.bfloat16, device=None):
+                 dtype: torch.dtype = torch.bfloat16, device=None, router_bias: bool = False, expert_act: str = "gelu"):
         super().__init__()
+        assert expert_act in ("gelu", "relu_sq"), expert_act
+        assert router_act != "softmax_top" or not (identity_experts or choice_bias), "softmax over the chosen logits: plain experts only"
+        self.expert_act = expert_act
         self.width, self.ff, self.experts, self.top, self.weight_scale, self.shared_ff = width, ff, experts, top, weight_scale, shared_ff
         self.gated, self.identity_experts = gated, identity_experts
-        self.router = RouterTopK(experts + identity_experts, top, width, dtype=torch.float32, device=device, act_fn=router_act)
+        self.router = RouterTopK(experts + identity_experts, top, width, dtype=torch.float32, device=device, bias=router_bias,
+                                 act_fn="softmax" if router_act == "softmax_top" else router_act,
+                                 apply_act_fn_over_topk=router_act == "softmax_top")
+        self.router_act = router_act
         self.router.requires_grad_(False)
         mk = lambda *s: nn.Parameter(torch.zeros(*s, dtype=dtype, device=device), requires_grad=False)
         self.up, self.down = mk(experts, (2 if gated else 1) * ff, width), mk(experts, width, ff)
@@ -49,28 +59,35 @@ class RoutedFFN(nn.Module):
         """Float logits.  When the activations are bfloat16 and the (float) router matrix holds only numbers that bfloat16 represents
         exactly — a checkpoint stored in bfloat16 — the product runs on the bfloat16 operands with float accumulation: the same
         products and a float sum, on the tensor cores.  Otherwise the framework router's float product."""
+        z = self._router_products(h)
+        b = self.router.linear_router.bias
+        return z if b is None else z + b
+
+    def _router_products(self, h: torch.Tensor) -> torch.Tensor:
         w = self.router.linear_router.weight
-        if h.is_cuda and h.shape[0] <= seqmix.SMALL_LINEAR_ROWS and self.router.linear_router.bias is None:
+        if h.is_cuda and h.shape[0] <= seqmix.SMALL_LINEAR_ROWS:
             return seqmix.linear_f32(h, w)                         # a warp per (row, expert): float products of the stored numbers
-        if h.dtype != torch.bfloat16 or not h.is_cuda or self.router.linear_router.bias is not None:
-            return self.router.get_router_logits(h)
+        if h.dtype != torch.bfloat16 or not h.is_cuda:
+            return F.linear(h.float(), w)
         if self._router_lowp is None or self._router_lowp[0] != w._version:
             low = w.detach().to(torch.bfloat16)
             self._router_lowp = (w._version, low.t().contiguous() if bool((low.float() == w).all()) else None)
         if self._router_lowp[1] is None:
-            return self.router.get_router_logits(h)
+            return F.linear(h.float(), w)
         return seqmix.matmul_f32(h[None], self._router_lowp[1][None])[0]
 
     def route(self, h: torch.Tensor):
         """Float scores of all experts → (weights ``[N, top]`` float, expert ids ``[N, top]``, identity share ``[N]`` float or None):
         one kernel for scores, correction, top-k and the identity experts' share (``seqmix.route_topk``)."""
-        w, idx, ident = seqmix.route_topk(self._router_logits(h), self.correction, self.top, self.experts, self.router.act_fn,
+        w, idx, ident = seqmix.route_topk(self._router_logits(h), self.correction, self.top, self.experts, self.router_act,
                                           self.weight_scale)
         return w, idx, (ident if self.identity_experts else None)
 
     def _act(self, y: torch.Tensor) -> torch.Tensor:
         """The experts' activation on the up-projection's output: ``[M, ff]`` (plain) or ``[M, 2 ff]`` → ``[M, ff]`` (gated)."""
-        return seqmix.silu_mul(y) if self.gated else seqmix.gelu_erf(y)
+        if self.gated:
+            return seqmix.silu_mul(y)
+        return seqmix.relu_sq(y) if self.expert_act == "relu_sq" else seqmix.gelu_erf(y)
 
     block_rows = 128               # rows per block of the grouped GEMM
 
@@ -118,7 +135,7 @@ class RoutedFFN(nn.Module):
         M = N * self.top
         if M <= self.small_batch_rows:
             sel = idx.reshape(-1).to(torch.int32)                  # the streaming kernels skip rows that name no matrix
-            mid = seqmix.indexed_gemv(self.up, sel, h.repeat_interleave(self.top, 0), "silu_glu" if self.gated else "gelu")
+            mid = seqmix.indexed_gemv(self.up, sel, h.repeat_interleave(self.top, 0), "silu_glu" if self.gated else self.expert_act)
             eo = seqmix.indexed_gemv(self.down, sel, mid, None)
             src = torch.arange(M, device=h.device, dtype=torch.int32).view(N, self.top)
         elif self._grouped_kernels(h) is not None:

@@ -132,3 +132,24 @@ class GainOnlyLayerNorm(nn.Module):
 
         seqmix.add_rms_norm_(res.view(-1, res.shape[-1]), y.reshape(-1, y.shape[-1]), self.weight, self.eps, center=True)
         return res
+
+
+class GatedPostRMSNorm(nn.Module):
+    """The closing step of a block whose norm comes AFTER the residual sum: ``x <- rms_norm(alpha * x + sigmoid(g) * y) * w`` on a
+    float stream ``x`` in place, with ``y`` the sublayer's result and ``g`` the logits of a gate per coordinate (``None``: no gate) that
+    the caller projects from the sublayer's input.  ``alpha`` weighs the skip path (deep post-norm stacks use ``alpha > 1``).
+    ``lowp`` receives the new stream rounded to the sublayers' dtype, ready to be the next sublayer's input (one kernel for all of
+    it, ``csrc/seqmix/norms.cu``)."""
+
+    def __init__(self, width: int, alpha: float = 1.0, eps: float = 1e-6, device=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(width, dtype=torch.float32, device=device), requires_grad=False)
+        self.alpha, self.eps = float(alpha), eps
+
+    def apply_(self, x: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor], lowp: Optional[torch.Tensor] = None) -> torch.Tensor:
+        from ..ops import seqmix
+
+        C = x.shape[-1]
+        seqmix.postnorm_gated_(x.view(-1, C), y.reshape(-1, C), None if gate is None else gate.reshape(-1, C), self.weight, self.alpha,
+                               self.eps, None if lowp is None else lowp.view(-1, C))
+        return x

@@ -30,11 +30,12 @@ CSRC = _ext.PKG_DIR.parent / "csrc" / "seqmix"
 GROUPS = {
     "core": (["short_conv.cu", "norms.cu", "activations.cu", "embed.cu", "rotary.cu", "bind_core.cpp"],
              ["short_conv", "rms_norm", "add_rms_norm_", "xielu", "gelu_erf", "silu_mul", "indexed_gemv", "moe_combine", "embed_sinusoid",
-              "group_rms_norm_gated", "route_topk", "small_linear_f32", "clamped_glu", "sigmoid_gate_mul_", "rotary_qkv_f32"]),
+              "group_rms_norm_gated", "route_topk", "small_linear_f32", "clamped_glu", "sigmoid_gate_mul_", "rotary_qkv_f32", "relu_sq",
+              "embed_bigram", "postnorm_gated_"]),
     "latent": (["latent_attention.cu", "latent_decode.cu", "latent_prefill.cu", "bind_latent.cpp"],
                ["latent_kv_store", "rope_q_", "latent_window_attention", "window_softmax", "latent_prompt_attention",
                 "latent_prompt_attention_fits"]),
-    "linrec": (["linear_recurrence.cu", "gla_chunked.cu", "bind_linrec.cpp"], ["gla_scan", "rglru_scan", "retention_scan"]),
+    "linrec": (["linear_recurrence.cu", "gla_chunked.cu", "bind_linrec.cpp"], ["gla_scan", "rglru_scan", "retention_scan", "mingru_scan"]),
     "headmix": (["headmix_attention.cu", "headmix_decode.cu", "headmix_prefill.cu", "bind_headmix.cpp"],
                 ["headmix_qk_prepare", "headmix_attention_prompt", "headmix_attention_token"]),
     "window": (["window_attention.cu", "window_prefill.cu", "bind_window.cpp"], ["window_qk_prepare", "window_attention_prompt", "window_attention_token"]),
@@ -174,11 +175,36 @@ def add_rms_norm_(res: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: floa
     return res
 
 
+def postnorm_gated_(x: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor], w: torch.Tensor, alpha: float, eps: float,
+                    lowp: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The closing step of a block whose norm comes after the residual sum, on the float stream ``x [rows, C]`` in place:
+    ``x <- rms_norm(alpha * x + sigmoid(gate) * y) * w`` (``gate`` None: ``alpha * x + y``).  ``y`` and ``gate`` are ``[rows, C]``
+    views of one dtype (row strides free); ``lowp`` (``[rows, C]`` of that dtype) receives a copy of the result."""
+    if _cuda(x):
+        _ext.count_launch()
+        ext().postnorm_gated_(x, y, gate, w, float(alpha), float(eps), lowp)
+        return x
+    v = alpha * x + (y.float() if gate is None else torch.sigmoid(gate.float()) * y.float())
+    x.copy_(v / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w)
+    if lowp is not None:
+        lowp.copy_(x.to(lowp.dtype))
+    return x
+
+
 # ---------------------------------------------------------------------------------------------------------------- latent attention
-def rotary_inv_freq(dims: int, base: float, device=None) -> torch.Tensor:
-    """``base^(-2i/dims)`` for i < dims/2, rounded once from float64."""
+def rotary_inv_freq(dims: int, base: float, device=None, scaling: Optional[dict] = None) -> torch.Tensor:
+    """``base^(-2i/dims)`` for i < dims/2, rounded once from float64.  ``scaling`` (``factor``, ``low``, ``high``, ``original``)
+    rescales them for a longer context by wavelength ``l = 2 pi / f``: kept where ``l < original / high``, divided by ``factor`` where
+    ``l > original / low``, and in between blended with ``s = (original / l - low) / (high - low)`` as
+    ``(1 - s) f / factor + s f``."""
     i = torch.arange(dims // 2, dtype=torch.float64)
-    return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims).float().to(device)
+    f = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims)
+    if scaling:
+        factor, low, high, orig = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+        wl = 2.0 * math.pi / f
+        s_ = (orig / wl - low) / (high - low) if high != low else torch.zeros_like(f)
+        f = torch.where(wl < orig / high, f, torch.where(wl > orig / low, f / factor, (1.0 - s_) * f / factor + s_ * f))
+    return f.float().to(device)
 
 
 def _rotate(x: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, dims: int) -> torch.Tensor:
@@ -309,17 +335,22 @@ def linear_f32(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 
 ROUTE_MAX_EXPERTS = 256
+ROUTE_KINDS = {"sigmoid": 0, "softmax": 1, "softmax_top": 2}
 
 
 def route_topk(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_real: int, act: str = "softmax", scale: float = 1.0):
     """Float router logits ``[N, E]`` → ``(weights [N, top] float, expert ids [N, top] int64, identity share [N] float)``.
     ``scores = softmax / sigmoid(logits)``; the ``top`` largest of ``scores + correction`` are chosen (descending); a chosen expert
     below ``n_real`` gets weight ``score * scale``, a chosen expert from ``n_real`` on (an identity expert) gets weight 0 and adds its
-    score to the row's identity share."""
+    score to the row's identity share.  ``act="softmax_top"``: the ``top`` largest LOGITS are chosen and the weights are the softmax
+    over the chosen logits only (times ``scale``); no correction, no identity experts."""
     if _cuda(logits) and logits.shape[1] <= ROUTE_MAX_EXPERTS:
         _ext.count_launch()
-        w, idx, ident = ext().route_topk(logits.contiguous(), correction, top, n_real, 1 if act == "softmax" else 0, float(scale))
+        w, idx, ident = ext().route_topk(logits.contiguous(), correction, top, n_real, ROUTE_KINDS[act], float(scale))
         return w, idx, ident
+    if act == "softmax_top":
+        val, idx = torch.topk(logits.float(), top, dim=-1)
+        return torch.softmax(val, -1) * scale, idx, torch.zeros(logits.shape[0], device=logits.device)
     scores = torch.softmax(logits.float(), -1) if act == "softmax" else torch.sigmoid(logits.float())
     idx = torch.topk(scores if correction is None else scores + correction, top, dim=-1).indices
     w = scores.gather(1, idx)
@@ -385,6 +416,29 @@ def rglru_scan(u: torch.Tensor, gr: torch.Tensor, gi: torch.Tensor, rbias: torch
     return out.to(u.dtype)
 
 
+def mingru_scan(z: torch.Tensor, u: torch.Tensor, g: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, lens: torch.Tensor,
+                fresh: bool) -> torch.Tensor:
+    """Minimal gated recurrent unit whose gates read only the current token.  Pre-activations ``z, u, g [B,S,W]`` (views with the same
+    strides) → ``[B,S,W]``: ``zt = sigmoid(z)``, candidate ``c = u + 1/2`` where ``u >= 0`` and ``sigmoid(u)`` below,
+    ``h_t = (1 - zt) h_(t-1) + zt c`` per channel, ``out = h_t * silu(g)``.  ``state [slots, W]`` float is read (unless ``fresh``) and
+    left at each row's last real token; gates, candidate and state are float."""
+    if _cuda(z):
+        _ext.count_launch()
+        return ext().mingru_scan(z, u, g, state, _i32(slots), _i32(lens), fresh)
+    B, S, W = z.shape
+    zf, uf, gf = z.float(), u.float(), g.float()
+    keep, take = torch.sigmoid(-zf), torch.sigmoid(zf)
+    cand = torch.where(uf >= 0, uf + 0.5, torch.sigmoid(uf))
+    h = torch.zeros(B, W) if fresh else state[slots.long()].clone()
+    out = torch.zeros(B, S, W)
+    for t in range(S):
+        live = (t < lens)[:, None]
+        h = torch.where(live, keep[:, t] * h + take[:, t] * cand[:, t], h)
+        out[:, t] = torch.where(live, h * F.silu(gf[:, t]), out[:, t])
+    state[slots.long()] = h
+    return out.to(z.dtype)
+
+
 # -------------------------------------------------------------------------------------------------- activations, routed small batch
 def xielu(x: torch.Tensor, ap: float, an: float) -> torch.Tensor:
     """``z > 0: ap z^2 + z/2``; ``z <= 0: an (exp(z) - 1 - z) + z/2``."""
@@ -402,12 +456,20 @@ def gelu_erf(x: torch.Tensor) -> torch.Tensor:
     return F.gelu(x.float()).to(x.dtype)
 
 
-GEMV_ACTS = {None: 0, "none": 0, "gelu": 1, "silu_glu": 2}
+def relu_sq(x: torch.Tensor) -> torch.Tensor:
+    """``max(x, 0)^2``."""
+    if _cuda(x):
+        _ext.count_launch()
+        return ext().relu_sq(x.contiguous())
+    return torch.relu(x.float()).pow(2).to(x.dtype)
+
+
+GEMV_ACTS = {None: 0, "none": 0, "gelu": 1, "silu_glu": 2, "relu_sq": 3}
 
 
 def indexed_gemv(w: torch.Tensor, sel: torch.Tensor, x: torch.Tensor, act) -> torch.Tensor:
     """``w [E,O,I]``, ``sel [M]``, ``x [M,I]`` → ``act(w[sel[m]] @ x[m])`` (float accumulation).  ``act``: ``None``, ``"gelu"`` (erf
-    form; ``True`` means the same) or ``"silu_glu"``: the matrix stacks gate rows over up rows and the result is
+    form; ``True`` means the same), ``"relu_sq"`` (the square of relu) or ``"silu_glu"``: the matrix stacks gate rows over up rows and the result is
     ``silu(gate) * up``, ``[M, O/2]``.  Rows whose ``sel`` names no matrix (``< 0`` or ``>= E``) give zeros."""
     kind = GEMV_ACTS["gelu" if act is True else (None if act is False else act)]
     if _cuda(x):
@@ -420,6 +482,8 @@ def indexed_gemv(w: torch.Tensor, sel: torch.Tensor, x: torch.Tensor, act) -> to
     elif kind == 2:
         half = y.shape[1] // 2
         y = F.silu(y[:, :half]) * y[:, half:]
+    elif kind == 3:
+        y = torch.relu(y).pow(2)
     return torch.where(ok[:, None], y, torch.zeros_like(y)).to(x.dtype)
 
 
@@ -465,6 +529,35 @@ def embed_sinusoid(tokens: torch.Tensor, table: torch.Tensor, scale: float, inv_
     return table[tokens].float() * scale + pe
 
 
+def embed_bigram(tokens: torch.Tensor, table: torch.Tensor, scale: float, pairs: Optional[torch.Tensor], mul_prev: int, mul_cur: int,
+                 prev: Optional[torch.Tensor], slots: torch.Tensor, lens: torch.Tensor, fresh: bool, want_lowp: bool = False):
+    """``tokens [B,S]`` → float ``[B,S,W]`` (and a copy in the table's dtype with ``want_lowp``): ``table[token] * scale`` plus
+    ``pairs[r]``, a table of ``buckets + 1`` rows indexed by a hash of the token and the one before it,
+    ``r = (previous * mul_prev + token * mul_cur) mod buckets``; a sequence's first token takes the last row.  ``prev [slots]``
+    (int64) carries each sequence's last token between calls: read for a row's first token unless ``fresh``, and left at the row's
+    last real token."""
+    if _cuda(table):
+        _ext.count_launch()
+        out, lp = ext().embed_bigram(tokens.contiguous(), table, float(scale), pairs, int(mul_prev), int(mul_cur), prev, _i32(slots), _i32(lens),
+                                     fresh, want_lowp)
+        return (out, lp) if want_lowp else (out, None)
+    B, S = tokens.shape
+    tok = tokens.long().clamp(0, table.shape[0] - 1)
+    out = table[tok].float() * scale
+    if pairs is not None:
+        buckets = pairs.shape[0] - 1
+        first = torch.full((B,), -1, dtype=torch.long) if (fresh or prev is None) else prev[slots.long()].clone()
+        before = torch.cat([first[:, None], tok[:, :-1]], 1)
+        row = torch.where(before < 0, torch.full_like(tok, buckets), (before * mul_prev + tok * mul_cur) % buckets)
+        out = out + pairs[row].float()
+    if prev is not None:
+        n = lens.long().clamp(max=S)
+        last = tok.gather(1, (n - 1).clamp(min=0)[:, None])[:, 0]
+        old = prev[slots.long()]
+        prev[slots.long()] = torch.where(n > 0, last, old)
+    return out, (out.to(table.dtype) if want_lowp else None)
+
+
 # ------------------------------------------------------------------------------------------------------------- grouped gated norm
 def group_rms_norm_gated(x: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, groups: int, eps: float, gate_first: bool,
                          out: Optional[torch.Tensor] = None, out_scale: float = 1.0, out_dtype: Optional[torch.dtype] = None,
@@ -493,23 +586,42 @@ def group_rms_norm_gated(x: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, g
 
 
 # ------------------------------------------------------------------------------------- grouped-query sliding-window attention
-def window_qk_prepare(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, qw: Optional[torch.Tensor], kw: Optional[torch.Tensor],
-                      eps: float, pos0: torch.Tensor, lens: torch.Tensor, slots: torch.Tensor, kcache: torch.Tensor,
-                      vcache: torch.Tensor) -> None:
-    """``q [B,S,H,D]``, ``k [B,S,G,D]``, ``v [B,S,G,V]`` (views; last dim contiguous): every head's query and key is divided by its
-    root mean square and multiplied by ``qw`` / ``kw`` (``[D]`` float; ``None``: left as they are) IN PLACE; the last ``ring``
-    real tokens of each row go to ``kcache [slots, ring, G, D]`` / ``vcache [slots, ring, G, V]`` at row ``position mod ring``."""
+def window_qk_prepare(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], qw: Optional[torch.Tensor],
+                      kw: Optional[torch.Tensor], eps: float, pos0: torch.Tensor, lens: torch.Tensor, slots: torch.Tensor,
+                      kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor], norm_all: bool = False,
+                      inv_freq: Optional[torch.Tensor] = None, rot_dims: int = 0) -> None:
+    """``q [B,S,H,D]``, ``k [B,S,G,D]``, ``v [B,S,G,V]`` (views; last dim contiguous), all IN PLACE.  Norm: every head's query and key
+    is divided by its root mean square and multiplied by ``qw`` / ``kw`` (``[D]`` float; ``None``: left as they are); with
+    ``norm_all`` the root mean square is taken over ALL heads of the token's queries (keys) at once and the weights hold ``H*D``
+    (``G*D``) numbers.  Rotation (``inv_freq [rot_dims/2]`` given): afterwards the first ``rot_dims`` coordinates of every query and
+    key head are rotated at position ``pos0[b] + t``, coordinate ``i`` paired with ``i + rot_dims/2``, angles in float.  The last
+    ``ring`` real tokens of each row go to ``kcache [slots, ring, G, D]`` / ``vcache [slots, ring, G, V]`` at row
+    ``position mod ring``.  ``k`` None (then ``v`` and the caches too): only the queries are prepared."""
     if _cuda(q):
         _ext.count_launch()
-        ext().window_qk_prepare(q, k, v, qw, kw, eps, _i32(pos0), _i32(lens), _i32(slots), kcache, vcache)
+        ext().window_qk_prepare(q, k, v, qw, kw, norm_all, eps, inv_freq, rot_dims if inv_freq is not None else 0, _i32(pos0), _i32(lens),
+                                _i32(slots), kcache, vcache)
         return
     B, S = q.shape[:2]
-    if qw is not None:
-        qf = q.float()
-        q.copy_((qf / torch.sqrt(qf.pow(2).mean(-1, keepdim=True) + eps) * qw).to(q.dtype))
-    if kw is not None:
-        kf = k.float()
-        k.copy_((kf / torch.sqrt(kf.pow(2).mean(-1, keepdim=True) + eps) * kw).to(k.dtype))
+    pos = (pos0.long()[:, None] + torch.arange(S)[None, :])[:, :, None]
+
+    def prep(x, w):
+        f = x.float()
+        if w is not None and norm_all:
+            flat = f.flatten(2)
+            f = (flat / torch.sqrt(flat.pow(2).mean(-1, keepdim=True) + eps) * w).view(f.shape)
+        elif w is not None:
+            f = f / torch.sqrt(f.pow(2).mean(-1, keepdim=True) + eps) * w
+        if inv_freq is not None and rot_dims:
+            f = _rotate(f, pos, inv_freq, rot_dims)
+        return f.to(x.dtype)
+
+    if qw is not None or inv_freq is not None:
+        q.copy_(prep(q, qw))
+    if k is None:
+        return
+    if kw is not None or inv_freq is not None:
+        k.copy_(prep(k, kw))
     ring = kcache.shape[1]
     for b in range(B):
         n, p0, sl = int(lens[b]), int(pos0[b]), int(slots[b])
@@ -522,23 +634,37 @@ def _capped(sc: torch.Tensor, softcap: float) -> torch.Tensor:
     return softcap * torch.tanh(sc / softcap) if softcap > 0 else sc
 
 
+def _window_weights(sc: torch.Tensor, ok: torch.Tensor, score_bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """``sc [B,H,...,keys]`` scores, ``ok`` broadcastable → weights: a softmax over the visible keys, or with ``score_bias [H]``
+    ``sigmoid(score + bias[h])`` of every visible key by itself."""
+    if score_bias is None:
+        return torch.nan_to_num(torch.softmax(sc.masked_fill(~ok, float("-inf")), -1), nan=0.0)
+    bias = score_bias.view((1, -1) + (1,) * (sc.dim() - 2))
+    return torch.sigmoid(sc + bias) * ok
+
+
 def window_attention_prompt(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: Optional[torch.Tensor], lens: torch.Tensor,
-                            window: int, scale: float, softcap: float, out: torch.Tensor, out_scale: float = 1.0) -> torch.Tensor:
+                            window: int, scale: float, softcap: float, out: torch.Tensor, out_scale: float = 1.0,
+                            score_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Prompts that start at position 0: ``q [B,S,H,D]``, ``k [B,S,G,D]``, ``v [B,S,G,V]`` (views), query head h uses key/value head
     ``h // (H/G)``; query i sees ``i - window < j <= i``.  Scores ``q.k * scale``, capped as ``softcap * tanh(score / softcap)``
-    when ``softcap > 0``, softmax in float.  Each head's result is multiplied by ``sigmoid(gate[b,s,h])`` (if given) and
-    ``out_scale`` and written to ``out [B*S, >= H*V]`` (row stride free); padded rows give zeros."""
+    when ``softcap > 0``, softmax in float; with ``score_bias [H]`` (float) the weight of a visible key is
+    ``sigmoid(score + score_bias[h])`` instead, not normalised over the keys.  Each head's result is multiplied by
+    ``sigmoid(gate[b,s,h])`` (if given) and ``out_scale`` and written to ``out [B*S, >= H*V]`` (row stride free); padded rows give
+    zeros."""
     if _cuda(q):
         _ext.count_launch()
-        ext().window_attention_prompt(q, k, v, gate, _i32(lens), window, scale, softcap, out, out_scale)
+        ext().window_attention_prompt(q, k, v, gate, _i32(lens), window, scale, softcap, score_bias, out, out_scale)
         return out
     B, S, H, D = q.shape
     G, V = k.shape[2], v.shape[3]
     kk, vv = k.float().repeat_interleave(H // G, 2), v.float().repeat_interleave(H // G, 2)
     sc = _capped(torch.einsum("bihd,bjhd->bhij", q.float(), kk) * scale, softcap)
     i, j = torch.arange(S)[:, None], torch.arange(S)[None, :]
-    sc = sc.masked_fill(~((j <= i) & (j > i - window)), float("-inf"))
-    o = torch.einsum("bhij,bjhv->bihv", torch.softmax(sc, -1), vv)
+    real = (torch.arange(S)[None, :] < lens[:, None])
+    vv = torch.where(real[..., None, None], vv, torch.zeros(()))
+    sc = torch.where(real[:, None, None, :], sc, torch.zeros(()))                               # padded rows hold anything
+    o = torch.einsum("bhij,bjhv->bihv", _window_weights(sc, ((j <= i) & (j > i - window))[None, None], score_bias), vv)
     if gate is not None:
         o = o * torch.sigmoid(gate.float())[..., None]
     o = torch.where((torch.arange(S)[None, :] < lens[:, None])[..., None, None], o * out_scale, torch.zeros_like(o))
@@ -548,13 +674,14 @@ def window_attention_prompt(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g
 
 def window_attention_token(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, gate: Optional[torch.Tensor], slots: torch.Tensor,
                            pos0: torch.Tensor, lens: torch.Tensor, window: int, scale: float, softcap: float, out: torch.Tensor,
-                           out_scale: float = 1.0) -> torch.Tensor:
+                           out_scale: float = 1.0, score_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Single tokens ``q [B,1,H,D]`` at positions ``pos0`` against their slots' rings (``kcache [slots, ring, G, D]``, ``vcache
-    [slots, ring, G, V]``; row ``j mod ring`` holds position j, the token's own row included).  Same scores, gate and output
-    layout as :func:`window_attention_prompt`; rows with ``lens == 0`` give zeros."""
+    [slots, ring, G, V]``; row ``j mod ring`` holds position j, the token's own row included; ``ring >= window``).  Same scores,
+    weights, gate and output layout as :func:`window_attention_prompt`; rows with ``lens == 0`` give zeros."""
     if _cuda(q):
         _ext.count_launch()
-        ext().window_attention_token(q, kcache, vcache, gate, _i32(slots), _i32(pos0), _i32(lens), window, scale, softcap, out, out_scale)
+        ext().window_attention_token(q, kcache, vcache, gate, _i32(slots), _i32(pos0), _i32(lens), window, scale, softcap, score_bias, out,
+                                     out_scale)
         return out
     B, _, H, D = q.shape
     ring, G, V = kcache.shape[1], kcache.shape[2], vcache.shape[3]
@@ -564,9 +691,9 @@ def window_attention_token(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.
     p = pos0.long()[:, None]
     m = torch.remainder(p - torch.arange(ring)[None, :], ring)                                      # distance back of ring row r
     ok = (p - m >= 0) & (m < window)
-    sc = sc.masked_fill(~ok[:, None, :], float("-inf"))
+    sc = torch.where(ok[:, None, :], sc, torch.zeros(()))
     vb = torch.where(ok[:, :, None, None], vb, torch.zeros_like(vb))                               # rows never written hold anything
-    o = torch.einsum("bhr,brhv->bhv", torch.softmax(sc, -1), vb)
+    o = torch.einsum("bhr,brhv->bhv", _window_weights(sc, ok[:, None, :], score_bias), vb)
     if gate is not None:
         o = o * torch.sigmoid(gate.float()).view(B, H, 1)
     o = torch.where((lens > 0)[:, None, None], o * out_scale, torch.zeros_like(o))
