@@ -100,7 +100,23 @@ Tensor rglru_scan(const Tensor& u, const Tensor& gr, const Tensor& gi, const Ten
     return out;
 }
 
+// zraw, uraw, graw [B,S,W]: views with the same strides (parts of one stacked projection) → out [B,S,W]; state [slots, W] float
+Tensor mingru_scan(const Tensor& z, const Tensor& u, const Tensor& g, Tensor state, const Tensor& slots, const Tensor& lens, bool fresh) {
+    TORCH_CHECK(z.is_cuda() && z.dim() == 3 && z.stride(2) == 1 && u.sizes() == z.sizes() && g.sizes() == z.sizes() && u.strides() == z.strides() &&
+                    g.strides() == z.strides() && u.scalar_type() == z.scalar_type() && g.scalar_type() == z.scalar_type(),
+                "z, u, g must be [B,S,W] views with the same strides and dtype");
+    const int B = z.size(0), S = z.size(1), W = z.size(2);
+    TORCH_CHECK(state.is_contiguous() && state.scalar_type() == at::kFloat && state.dim() == 2 && state.size(1) == W, "state must be float [slots, W]");
+    TORCH_CHECK(slots.numel() == B && lens.numel() == B, "one slot and one length per row");
+    Tensor out = at::empty({B, S, W}, z.options());
+    seqmix::mingru_scan(z.data_ptr(), u.data_ptr(), g.data_ptr(), is_bf(z), z.stride(0), z.stride(1), state.data_ptr<float>(), i32(slots),
+                        i32(lens), fresh, B, S, W, out.data_ptr(), stream());
+    check_launch();
+    return out;
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("mingru_scan", &mingru_scan);
     m.def("gla_scan", &gla_scan);
     m.def("retention_scan", &retention_scan);
     m.def("rglru_scan", &rglru_scan);

@@ -7,9 +7,15 @@
 //               the step's alpha / k / q / v are staged through shared memory (double buffered: one barrier per token).
 //   rglru_scan: per channel  a = exp(-8 r softplus(lam)),  h_t = a h_(t-1) + sqrt(1 - a^2) i u_t,  out = h_t * gelu_tanh(y)
 //               with r, i = sigmoid(gate pre-activations + bias); sqrt(1 - a^2) is formed as sqrt(-expm1(2 log a)).
+//   mingru_scan: per channel h_t = (1 - z) h_(t-1) + z c with z = sigmoid(zraw) and the candidate c = uraw + 1/2 (uraw >= 0) or
+//               sigmoid(uraw) (below), out = h_t * silu(graw)
 // Tokens at or past lens[b] are padding: they write zeros and do not touch the state.
+#include <cooperative_groups.h>
+
 #include "seq_common.cuh"
 #include "seqmix.h"
+
+namespace cg = cooperative_groups;
 
 namespace seqmix {
 
@@ -298,6 +304,166 @@ void rglru_scan(const void* u, int bf, const float* gr, const float* gi, int wb,
                                                           state, slots, lens, fresh, B, S, W, (bf16*)out);
     else rglru_scan_kernel<float><<<grid, block, 0, s>>>((const float*)u, gr, gi, wb, rbias, ibias, lam_sp, (const float*)y, y_sb, y_st,
                                                          state, slots, lens, fresh, B, S, W, (float*)out);
+}
+
+// minGRU: per channel h_t = (1 - z_t) h_(t-1) + z_t c_t with z = sigmoid(zraw), c = uraw + 1/2 where uraw >= 0 and sigmoid(uraw) below,
+// out_t = h_t * silu(graw_t); the gates read only the current token, so the same two-pass scan as the real-gated LRU applies: each
+// time lane scans its slice from zero keeping the product of its (1 - z), the carries are folded through shared memory, the lanes
+// scan again from their true carry.  One block = 32 * CPT channels of one sequence x TY time lanes; gates, candidate and state in
+// float.  sigmoid(z) and 1 - sigmoid(z) = sigmoid(-z) come from ONE exponential of -|z| and one reciprocal, both exact to rounding.
+// FAST (the bfloat16 instantiation, whose inputs carry 8 bits): the exponential and the reciprocal are the hardware approximations
+// (relative error about 1e-6, far below the inputs' rounding); the float instantiation uses the exact-rounded library functions.
+// CPT = 2: a thread owns two neighbouring channels and reads them as one 4-byte pair.
+template <bool FAST> __device__ __forceinline__ float exp_neg_(float x) { return FAST ? __expf(x) : expf(x); }
+template <bool FAST> __device__ __forceinline__ float rcp1p_(float e) { return FAST ? __fdividef(1.f, 1.f + e) : 1.f / (1.f + e); }
+template <bool FAST> __device__ __forceinline__ void sigmoid_pair_(float z, float& s, float& a) {       // s = sigmoid(z), a = sigmoid(-z)
+    const float e = exp_neg_<FAST>(-fabsf(z)), r = rcp1p_<FAST>(e), er = e * r;
+    s = z >= 0.f ? r : er;
+    a = z >= 0.f ? er : r;
+}
+template <bool FAST> __device__ __forceinline__ float mingru_candidate_(float u) {
+    const float e = exp_neg_<FAST>(fminf(u, 0.f));
+    return u >= 0.f ? u + 0.5f : e * rcp1p_<FAST>(e);
+}
+template <int CPT, typename T> __device__ __forceinline__ void ld_ch(const T* p, float (&v)[CPT]) {
+    if (CPT == 1) v[0] = ldf(p);
+    else {
+        const __nv_bfloat162 t = *reinterpret_cast<const __nv_bfloat162*>(p);      // CPT == 2 is only instantiated for bfloat16
+        v[0] = __low2float(t); v[CPT - 1] = __high2float(t);
+    }
+}
+template <int CPT, typename T> __device__ __forceinline__ void st_ch(T* p, const float (&v)[CPT]) {
+    if (CPT == 1) stf(p, v[0]);
+    else *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[CPT - 1]);
+}
+
+// CL: the time lanes of a sequence's channels are blockDim.y lanes in each of gridDim.z blocks that form ONE thread-block cluster
+// (so that a long prompt of few sequences still fills the GPU): every block folds its lanes' carries into one pair per channel, the
+// blocks read the pairs of the blocks before them through distributed shared memory.  Every thread reaches both cluster barriers.
+template <typename T, int CPT, bool FAST, bool CL>
+__global__ void __launch_bounds__(1024, 2) mingru_scan_kernel(const T* __restrict__ z, const T* __restrict__ u, const T* __restrict__ g, long sb, long st,
+                                   float* state, const int* __restrict__ slots, const int* __restrict__ lens, int fresh, int S, int W,
+                                   T* __restrict__ out) {
+    __shared__ float sA[CPT][32][33], sH[CPT][32][33], cA[CPT][32], cH[CPT][32];
+    const int c = (blockIdx.x * 32 + threadIdx.x) * CPT, b = blockIdx.y, ty = threadIdx.y, TY = blockDim.y;
+    const int cz = CL ? blockIdx.z : 0, lanes = CL ? TY * gridDim.z : TY, gl = cz * TY + ty;   // the cluster spans the grid's z extent
+    const int len = min(lens[b], S);
+    const int L = (len + lanes - 1) / lanes, t0 = min(len, gl * L), t1 = min(len, t0 + L);
+    const bool on = c < W;                                   // W is a multiple of CPT: a thread's channels are all in or all out
+    const long base = (long)b * sb + c;
+    float A[CPT], h[CPT];
+#pragma unroll
+    for (int k = 0; k < CPT; ++k) { A[k] = 1.f; h[k] = 0.f; }
+    if (on && lanes > 1) {
+#pragma unroll 4
+        for (int t = t0; t < t1; ++t) {
+            float zr[CPT], ur[CPT];
+            ld_ch<CPT>(z + base + (long)t * st, zr);
+            ld_ch<CPT>(u + base + (long)t * st, ur);
+#pragma unroll
+            for (int k = 0; k < CPT; ++k) {
+                float sg, a;
+                sigmoid_pair_<FAST>(zr[k], sg, a);
+                h[k] = fmaf(a, h[k], sg * mingru_candidate_<FAST>(ur[k]));
+                A[k] *= a;
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < CPT; ++k) { sA[k][ty][threadIdx.x] = A[k]; sH[k][ty][threadIdx.x] = h[k]; }
+    __syncthreads();
+    if (CL && ty == TY - 1) {                                // this block's lanes as one pair per channel
+#pragma unroll
+        for (int k = 0; k < CPT; ++k) {
+            float a = 1.f, x = 0.f;
+            for (int j = 0; j < TY; ++j) { x = fmaf(sA[k][j][threadIdx.x], x, sH[k][j][threadIdx.x]); a *= sA[k][j][threadIdx.x]; }
+            cA[k][threadIdx.x] = a; cH[k][threadIdx.x] = x;
+        }
+    }
+    if (CL) cg::this_cluster().sync();
+    float* hs = state + (long)(on ? slots[b] : 0) * W + (on ? c : 0);
+    if (on) {
+#pragma unroll
+        for (int k = 0; k < CPT; ++k) {
+            h[k] = fresh ? 0.f : hs[k];
+            if (CL) {
+                cg::cluster_group cluster = cg::this_cluster();
+                for (int r = 0; r < cz; ++r) {
+                    const float* ra = cluster.map_shared_rank(&cA[k][threadIdx.x], r);
+                    const float* rh = cluster.map_shared_rank(&cH[k][threadIdx.x], r);
+                    h[k] = fmaf(*ra, h[k], *rh);
+                }
+            }
+            for (int j = 0; j < ty; ++j) h[k] = fmaf(sA[k][j][threadIdx.x], h[k], sH[k][j][threadIdx.x]);
+        }
+#pragma unroll 4
+        for (int t = t0; t < t1; ++t) {
+            float zr[CPT], ur[CPT], gr[CPT], o[CPT];
+            ld_ch<CPT>(z + base + (long)t * st, zr);
+            ld_ch<CPT>(u + base + (long)t * st, ur);
+            ld_ch<CPT>(g + base + (long)t * st, gr);
+#pragma unroll
+            for (int k = 0; k < CPT; ++k) {
+                float sg, a, gs, gn;
+                sigmoid_pair_<FAST>(zr[k], sg, a);
+                h[k] = fmaf(a, h[k], sg * mingru_candidate_<FAST>(ur[k]));
+                sigmoid_pair_<FAST>(gr[k], gs, gn);
+                o[k] = h[k] * gr[k] * gs;
+            }
+            st_ch<CPT>(out + ((long)b * S + t) * W + c, o);
+        }
+        float zero[CPT];
+#pragma unroll
+        for (int k = 0; k < CPT; ++k) zero[k] = 0.f;
+        for (int t = len + gl; t < S; t += lanes) st_ch<CPT>(out + ((long)b * S + t) * W + c, zero);
+    }
+    if (CL) cg::this_cluster().sync();   // no block leaves while another may still read its pairs; the state's old value has been read
+    if (on && gl == lanes - 1)       // the last lane's slice ends at the sequence's last token (an empty slice passes the carry on)
+#pragma unroll
+        for (int k = 0; k < CPT; ++k) hs[k] = h[k];
+}
+
+template <typename T, int CPT, bool FAST>
+static void mingru_launch(dim3 grid, dim3 block, const void* z, const void* u, const void* g, long sb, long st, float* state, const int* slots,
+                          const int* lens, int fresh, int S, int W, void* out, cudaStream_t s) {
+    if (grid.z == 1) {
+        mingru_scan_kernel<T, CPT, FAST, false><<<grid, block, 0, s>>>((const T*)z, (const T*)u, (const T*)g, sb, st, state, slots, lens, fresh,
+                                                                       S, W, (T*)out);
+        return;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = 0; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = grid.z;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, mingru_scan_kernel<T, CPT, FAST, true>, (const T*)z, (const T*)u, (const T*)g, sb, st, state, slots, lens, fresh, S, W,
+                       (T*)out);
+}
+
+void mingru_scan(const void* z, const void* u, const void* g, int bf, long sb, long st, float* state, const int* slots, const int* lens,
+                 int fresh, int B, int S, int W, void* out, cudaStream_t s) {
+    if (B * S * W == 0) return;
+    int ty = 1;
+    while (ty < 32 && ty * 16 < S) ty <<= 1;
+    int cz_most = 1;                                         // blocks per cluster: a lane keeps at least 16 tokens; 8 is the portable limit
+    while (cz_most < 8 && ty * cz_most * 2 * 16 <= S) cz_most <<= 1;
+    auto shape = [&](int cpt, int& cz) {                     // blocks of the launch with cpt channels per thread
+        const int base = (W + 32 * cpt - 1) / (32 * cpt) * B;
+        cz = 1;
+        while (cz < cz_most && base * cz < 148) cz <<= 1;    // clusters only while a block per SM is not reached
+        return base * cz;
+    };
+    auto a4 = [](const void* p) { return (uintptr_t)p % 4 == 0; };
+    int cz2 = 1, cz1 = 1;
+    const bool can_pair = bf && W % 2 == 0 && sb % 2 == 0 && st % 2 == 0 && a4(z) && a4(u) && a4(g) && a4(out);
+    const bool pairs = can_pair && shape(2, cz2) >= 148;     // two channels per thread where that still fills the GPU
+    shape(1, cz1);
+    const int cz = pairs ? cz2 : cz1;
+    dim3 block(32, ty), grid((W + (pairs ? 63 : 31)) / (pairs ? 64 : 32), B, cz);
+    if (pairs) mingru_launch<bf16, 2, true>(grid, block, z, u, g, sb, st, state, slots, lens, fresh, S, W, out, s);
+    else if (bf) mingru_launch<bf16, 1, true>(grid, block, z, u, g, sb, st, state, slots, lens, fresh, S, W, out, s);
+    else mingru_launch<float, 1, false>(grid, block, z, u, g, sb, st, state, slots, lens, fresh, S, W, out, s);
 }
 
 }  // namespace seqmix
