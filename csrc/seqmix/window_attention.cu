@@ -1,9 +1,13 @@
-// Grouped-query softmax attention over a sliding window (no positional rotation): query position i sees i - window < j <= i;
-// query head h reads key/value head h / (H/G).  Scores are q.k * scale, capped as softcap * tanh(score / softcap) when softcap > 0;
-// scores, softmax weights and sums are float.  Each head's result may be multiplied by sigmoid(gate[b,t,h]) and a constant before
-// it is written (row stride free: several mixers write side by side into one buffer).
-//   window_qk_prepare      : RMS norm per head of queries and keys in place (one weight vector each), and the last `ring` real
-//                            tokens' keys and values to the sequence's ring rows (position mod ring)
+// Grouped-query attention over a sliding window: query position i sees i - window < j <= i; query head h reads key/value head
+// h / (H/G).  Scores are q.k * scale, capped as softcap * tanh(score / softcap) when softcap > 0; scores, weights and sums are
+// float.  The weights are a softmax over the visible keys, or — when a score bias per head is given — sigmoid(score + bias[h]) of
+// each visible key by itself, not normalised over the keys.  Each head's result may be multiplied by sigmoid(gate[b,t,h]) and a
+// constant before it is written (row stride free: several mixers write side by side into one buffer).
+//   window_qk_prepare      : RMS norm of queries and keys in place, per head (one weight vector of D numbers each) or over the whole
+//                            projection at once (weights of H*D and G*D numbers); then, when frequencies are given, rotation of the
+//                            first `dims` coordinates of every head at the token's position (pairs i, i + dims/2; angles in float);
+//                            and the last `ring` real tokens' keys and values to the sequence's ring rows (position mod ring);
+//                            with no keys given only the queries are prepared (a layer that reads another layer's ring)
 //   window_attention_prompt: prompts starting at position 0, keys and values of the call itself.  A block owns 16 consecutive
 //                            queries of one head (4 warps x 4 queries); key / value rows come through shared memory 32 at a time;
 //                            in the score pass a lane owns one key (4 queries per shared-memory read), in the value pass a lane
@@ -21,33 +25,64 @@ namespace seqmix {
 
 template <typename T>
 __global__ void window_qk_prepare_kernel(T* q, long q_sb, long q_st, T* k, long k_sb, long k_st, const T* __restrict__ v, long v_sb,
-                                         long v_st, const float* __restrict__ qw, const float* __restrict__ kw, float eps,
-                                         const int* __restrict__ pos0, const int* __restrict__ lens, const int* __restrict__ slots,
-                                         T* kcache, T* vcache, int ring, int S, int H, int G, int D, int V) {
+                                         long v_st, const float* __restrict__ qw, const float* __restrict__ kw, int norm_all, float eps,
+                                         const float* __restrict__ inv_freq, int dims, const int* __restrict__ pos0,
+                                         const int* __restrict__ lens, const int* __restrict__ slots, T* kcache, T* vcache, int ring, int S,
+                                         int H, int G, int D, int V) {
+    __shared__ float red[2][8];
     const int row = blockIdx.x, b = row / S, t = row - b * S, lane = threadIdx.x;
     const int len = min(lens[b], S);
     if (t >= len) return;
-    const bool keep = t >= len - ring;
-    const long cr = ((long)slots[b] * ring + (pos0[b] + t) % ring) * G;
-    for (int u = threadIdx.y; u < H + 2 * G; u += blockDim.y) {
+    const bool keep = k != nullptr && t >= len - ring;
+    const int pos = pos0[b] + t, half = inv_freq ? dims / 2 : 0, rot = 2 * half;
+    const long cr = k ? ((long)slots[b] * ring + pos % ring) * G : 0;
+    T* qrow = q + (long)b * q_sb + (long)t * q_st;
+    T* krow = k ? k + (long)b * k_sb + (long)t * k_st : nullptr;
+    float inv_all[2] = {1.f, 1.f};
+    if (norm_all) {                                          // one statistic over all heads of the queries, one over all of the keys
+        const int tid = threadIdx.y * 32 + lane, nthr = blockDim.y * 32;
+        float sq = 0.f, sk = 0.f;
+        if (qw) for (int x = tid; x < H * D; x += nthr) { const float e = ldf(qrow + x); sq = fmaf(e, e, sq); }
+        if (kw && krow) for (int x = tid; x < G * D; x += nthr) { const float e = ldf(krow + x); sk = fmaf(e, e, sk); }
+        sq = warp_sum(sq); sk = warp_sum(sk);
+        if (lane == 0) { red[0][threadIdx.y] = sq; red[1][threadIdx.y] = sk; }
+        __syncthreads();
+        sq = sk = 0.f;
+        for (int x = 0; x < (int)blockDim.y; ++x) { sq += red[0][x]; sk += red[1][x]; }
+        inv_all[0] = 1.f / sqrtf(sq / (float)(H * D) + eps);
+        inv_all[1] = 1.f / sqrtf(sk / (float)(G * D) + eps);
+    }
+    const int units = krow ? H + 2 * G : H;
+    for (int u = threadIdx.y; u < units; u += blockDim.y) {
         if (u < H + G) {
             const bool isq = u < H;
             const int hh = isq ? u : u - H;
-            T* p = isq ? q + (long)b * q_sb + (long)t * q_st + (long)hh * D : k + (long)b * k_sb + (long)t * k_st + (long)hh * D;
+            T* p = (isq ? qrow : krow) + (long)hh * D;
             const float* w = isq ? qw : kw;
             T* dst = (!isq && keep) ? kcache + (cr + hh) * D : nullptr;
             float inv = 1.f;
-            if (w) {
+            if (w && norm_all) {
+                inv = inv_all[isq ? 0 : 1];
+                w += (long)hh * D;
+            } else if (w) {
                 float ss = 0.f;
                 for (int d = lane; d < D; d += 32) { const float x = ldf(p + d); ss = fmaf(x, x, ss); }
                 inv = 1.f / sqrtf(warp_sum(ss) / (float)D + eps);
             }
-            if (w || dst) {
-                for (int d = lane; d < D; d += 32) {
-                    const float x = w ? ldf(p + d) * inv * w[d] : ldf(p + d);
-                    if (w) stf(p + d, x);
-                    if (dst) stf(dst + d, x);
-                }
+            if (!(w || dst || rot)) continue;
+            for (int i = lane; i < half; i += 32) {          // a lane reads both members of a pair before it writes them
+                float x0 = ldf(p + i), x1 = ldf(p + i + half);
+                if (w) { x0 *= inv * w[i]; x1 *= inv * w[i + half]; }
+                float sn, cs;
+                sincosf((float)pos * inv_freq[i], &sn, &cs);
+                const float y0 = x0 * cs - x1 * sn, y1 = x1 * cs + x0 * sn;
+                stf(p + i, y0); stf(p + i + half, y1);
+                if (dst) { stf(dst + i, y0); stf(dst + i + half, y1); }
+            }
+            for (int d = rot + lane; d < D; d += 32) {
+                const float x = w ? ldf(p + d) * inv * w[d] : ldf(p + d);
+                if (w) stf(p + d, x);
+                if (dst) stf(dst + d, x);
             }
         } else if (keep) {
             const int hh = u - H - G;
@@ -69,7 +104,7 @@ template <typename T, int VPL>
 __global__ void __launch_bounds__(128) window_prompt_kernel(
     const T* __restrict__ q, long q_sb, long q_st, const T* __restrict__ k, long k_sb, long k_st, const T* __restrict__ v, long v_sb,
     long v_st, const T* __restrict__ gate, long g_sb, long g_st, const int* __restrict__ lens, int S, int H, int G, int D, int V,
-    int window, float scale, float softcap, T* __restrict__ out, long out_stride, float out_scale) {
+    int window, float scale, float softcap, const float* __restrict__ score_bias, T* __restrict__ out, long out_stride, float out_scale) {
     extern __shared__ float sm[];
     const int DP = D + 1;
     float* Ks = sm;
@@ -77,6 +112,8 @@ __global__ void __launch_bounds__(128) window_prompt_kernel(
     float* Qs = Vs + kKeys * V;
     float* Ps = Qs + kWarps * D * kQW;
     const int i0 = blockIdx.x * (kWarps * kQW), h = blockIdx.y, b = blockIdx.z, g = h / (H / G);
+    const bool sig = score_bias != nullptr;                          // independent sigmoid weights instead of a softmax
+    const float sbias = sig ? score_bias[h] : 0.f;
     const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
     const int len = min(lens[b], S);
     const int iq0 = i0 + wp * kQW;                                   // this warp's first query position
@@ -127,6 +164,11 @@ __global__ void __launch_bounds__(128) window_prompt_kernel(
             const int i = iq0 + rq;
             const bool ok = i < len && j <= i && j > i - window;
             const float sc = ok ? cap_score(s[rq] * scale, softcap, inv_cap) : -INFINITY;
+            if (sig) {
+                corr[rq] = 1.f;
+                Pw[lane * kQW + rq] = ok ? sigmoidf_(sc + sbias) : 0.f;
+                continue;
+            }
             float mx = sc;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -158,7 +200,7 @@ __global__ void __launch_bounds__(128) window_prompt_kernel(
     for (int rq = 0; rq < kQW; ++rq) {
         const int i = iq0 + rq;
         if (i >= S) continue;
-        const float lt = warp_sum(l[rq]);
+        const float lt = sig ? 1.f : warp_sum(l[rq]);
         float f = 0.f;
         if (i < len && lt > 0.f) {
             f = out_scale / lt;
@@ -208,7 +250,8 @@ template <typename T, int VPL, bool VEC>
 __global__ void __launch_bounds__(128) window_token_kernel(
     const T* __restrict__ q, long q_sb, const T* __restrict__ kcache, const T* __restrict__ vcache, const int* __restrict__ slots,
     const int* __restrict__ pos0, const int* __restrict__ lens, int ring, int H, int G, int D, int V, int window, float scale,
-    float softcap, int splits, float* __restrict__ part_m, float* __restrict__ part_l, float* __restrict__ part_acc) {
+    float softcap, const float* __restrict__ score_bias, int splits, float* __restrict__ part_m, float* __restrict__ part_l,
+    float* __restrict__ part_acc) {
     extern __shared__ float sm[];
     const int DP = D + 1;
     float* Ks = sm;
@@ -220,6 +263,8 @@ __global__ void __launch_bounds__(128) window_token_kernel(
     const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
     const bool has = hq + wp < HG;                                   // this warp has a head
     const int h = g * HG + hq + wp;
+    const bool sig = score_bias != nullptr;                          // independent sigmoid weights: the partial results are plain sums
+    const float sbias = (sig && has) ? score_bias[h] : 0.f;
     const int p = pos0[b];
     const int rows = lens[b] > 0 ? min(ring, p + 1) : 0;             // ring rows that hold a position (rows 0..p before the ring wraps)
     int per = (rows + splits - 1) / splits;
@@ -249,14 +294,20 @@ __global__ void __launch_bounds__(128) window_token_kernel(
         if (back < 0) back += ring;
         const bool ok = rr < r1 && back < window && p - back >= 0;
         const float sc = ok ? cap_score(s * scale, softcap, inv_cap) : -INFINITY;
-        float mx = sc;
+        float pr, corr;
+        if (sig) {
+            pr = ok ? sigmoidf_(sc + sbias) : 0.f;
+            corr = 1.f;
+        } else {
+            float mx = sc;
 #pragma unroll
-        for (int w = 16; w > 0; w >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, w));
-        const float mn = fmaxf(m, mx);
-        const float pr = (ok && mn > -INFINITY) ? expf(sc - mn) : 0.f;
-        const float corr = (m > -INFINITY) ? expf(m - mn) : 0.f;
-        m = mn;
-        l = fmaf(l, corr, pr);
+            for (int w = 16; w > 0; w >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, w));
+            const float mn = fmaxf(m, mx);
+            pr = (ok && mn > -INFINITY) ? expf(sc - mn) : 0.f;
+            corr = (m > -INFINITY) ? expf(m - mn) : 0.f;
+            m = mn;
+            l = fmaf(l, corr, pr);
+        }
         Pw[lane] = pr;
 #pragma unroll
         for (int c = 0; c < VPL; ++c) acc[c] *= corr;
@@ -273,6 +324,7 @@ __global__ void __launch_bounds__(128) window_token_kernel(
     }
     if (!has) return;
     l = warp_sum(l);
+    if (sig) { m = 0.f; l = split == 0 ? 1.f : 0.f; }              // the merge then adds the stretches' sums and divides by one
     const long o = ((long)b * H + h) * splits + split;
     if (lane == 0) { part_m[o] = m; part_l[o] = l; }
 #pragma unroll
@@ -305,16 +357,19 @@ __global__ void window_token_merge_kernel(const float* __restrict__ part_m, cons
 }
 
 void window_qk_prepare(void* q, long q_sb, long q_st, void* k, long k_sb, long k_st, const void* v, long v_sb, long v_st, int bf,
-                       const float* qw, const float* kw, float eps, const int* pos0, const int* lens, const int* slots, void* kcache,
-                       void* vcache, int ring, int B, int S, int H, int G, int D, int V, cudaStream_t s) {
+                       const float* qw, const float* kw, int norm_all, float eps, const float* inv_freq, int dims, const int* pos0,
+                       const int* lens, const int* slots, void* kcache, void* vcache, int ring, int B, int S, int H, int G, int D, int V,
+                       cudaStream_t s) {
     if (B * S == 0) return;
     dim3 grid(B * S), block(32, 8);
     if (bf)
-        window_qk_prepare_kernel<bf16><<<grid, block, 0, s>>>((bf16*)q, q_sb, q_st, (bf16*)k, k_sb, k_st, (const bf16*)v, v_sb, v_st, qw, kw, eps,
-                                                             pos0, lens, slots, (bf16*)kcache, (bf16*)vcache, ring, S, H, G, D, V);
+        window_qk_prepare_kernel<bf16><<<grid, block, 0, s>>>((bf16*)q, q_sb, q_st, (bf16*)k, k_sb, k_st, (const bf16*)v, v_sb, v_st, qw, kw,
+                                                             norm_all, eps, inv_freq, dims, pos0, lens, slots, (bf16*)kcache, (bf16*)vcache,
+                                                             ring, S, H, G, D, V);
     else
         window_qk_prepare_kernel<float><<<grid, block, 0, s>>>((float*)q, q_sb, q_st, (float*)k, k_sb, k_st, (const float*)v, v_sb, v_st, qw, kw,
-                                                              eps, pos0, lens, slots, (float*)kcache, (float*)vcache, ring, S, H, G, D, V);
+                                                              norm_all, eps, inv_freq, dims, pos0, lens, slots, (float*)kcache,
+                                                              (float*)vcache, ring, S, H, G, D, V);
 }
 
 static int value_cols_per_lane(int V) { return V <= 64 ? 2 : (V <= 128 ? 4 : (V <= 256 ? 8 : (V <= 512 ? 16 : 0))); }
@@ -327,13 +382,14 @@ static bool raise_smem(K kernel, size_t smem) {
 
 bool window_attention_prompt(const void* q, long q_sb, long q_st, const void* k, long k_sb, long k_st, const void* v, long v_sb, long v_st,
                              const void* gate, long g_sb, long g_st, int bf, const int* lens, int B, int S, int H, int G, int D, int V,
-                             int window, float scale, float softcap, void* out, long out_stride, float out_scale, cudaStream_t s) {
+                             int window, float scale, float softcap, const float* score_bias, void* out, long out_stride, float out_scale,
+                             cudaStream_t s) {
     const int vpl = value_cols_per_lane(V);
     if (!vpl) return false;
     if (B * S == 0) return true;
     if (bf && window_prompt_mma_fits(q, q_sb, q_st, k, k_sb, k_st, v, v_sb, v_st, D, V, out, out_stride)) {
-        window_prompt_mma(q, q_sb, q_st, k, k_sb, k_st, v, v_sb, v_st, gate, g_sb, g_st, lens, B, S, H, G, D, V, window, scale, softcap, out,
-                          out_stride, out_scale, s);
+        window_prompt_mma(q, q_sb, q_st, k, k_sb, k_st, v, v_sb, v_st, gate, g_sb, g_st, lens, B, S, H, G, D, V, window, scale, softcap,
+                          score_bias, out, out_stride, out_scale, s);
         return true;
     }
     const size_t smem = sizeof(float) * ((size_t)kKeys * (D + 1) + (size_t)kKeys * V + (size_t)kWarps * D * kQW + kWarps * kKeys * kQW);
@@ -343,7 +399,7 @@ bool window_attention_prompt(const void* q, long q_sb, long q_st, const void* k,
         if (!raise_smem(window_prompt_kernel<T, P>, smem)) return false;                                                              \
         window_prompt_kernel<T, P><<<grid, block, smem, s>>>((const T*)q, q_sb, q_st, (const T*)k, k_sb, k_st, (const T*)v, v_sb, v_st,   \
                                                              (const T*)gate, g_sb, g_st, lens, S, H, G, D, V, window, scale, softcap,   \
-                                                             (T*)out, out_stride, out_scale);                                         \
+                                                             score_bias, (T*)out, out_stride, out_scale);                             \
     } while (0)
 #define SEQMIX_WP_T(P) do { if (bf) SEQMIX_WP(bf16, P); else SEQMIX_WP(float, P); } while (0)
     if (vpl == 2) SEQMIX_WP_T(2); else if (vpl == 4) SEQMIX_WP_T(4); else if (vpl == 8) SEQMIX_WP_T(8); else SEQMIX_WP_T(16);
@@ -361,8 +417,8 @@ int window_token_splits(int ring, int B, int H, int G) {
 
 bool window_attention_token(const void* q, long q_sb, const void* kcache, const void* vcache, const void* gate, long g_sb, int bf,
                             const int* slots, const int* pos0, const int* lens, int ring, int B, int H, int G, int D, int V, int window,
-                            float scale, float softcap, int splits, float* part_m, float* part_l, float* part_acc, void* out,
-                            long out_stride, float out_scale, cudaStream_t s) {
+                            float scale, float softcap, const float* score_bias, int splits, float* part_m, float* part_l, float* part_acc,
+                            void* out, long out_stride, float out_scale, cudaStream_t s) {
     const int vpl = value_cols_per_lane(V);
     if (!vpl) return false;
     if (B == 0) return true;
@@ -374,8 +430,8 @@ bool window_attention_token(const void* q, long q_sb, const void* kcache, const 
     do {                                                                                                                              \
         if (!raise_smem(window_token_kernel<T, P, VC>, smem)) return false;                                                           \
         window_token_kernel<T, P, VC><<<grid, block, smem, s>>>((const T*)q, q_sb, (const T*)kcache, (const T*)vcache, slots, pos0, lens, \
-                                                                ring, H, G, D, V, window, scale, softcap, splits, part_m, part_l,      \
-                                                                part_acc);                                                            \
+                                                                ring, H, G, D, V, window, scale, softcap, score_bias, splits, part_m,  \
+                                                                part_l, part_acc);                                                    \
     } while (0)
 #define SEQMIX_WT_V(T, P) do { if (vec) SEQMIX_WT(T, P, true); else SEQMIX_WT(T, P, false); } while (0)
 #define SEQMIX_WT_T(P) do { if (bf) SEQMIX_WT_V(bf16, P); else SEQMIX_WT_V(float, P); } while (0)

@@ -6,6 +6,7 @@
 // exponential), masked and exponentiated in float with a running maximum and sum per query; the weights are rounded to bfloat16
 // only as operands of the value product, whose accumulator is float.  The result is multiplied by sigmoid(gate) and a constant and
 // written with a free row stride.  Position i sees j with 0 <= i - j < window.  Queries at or past lens[b] give zeros.
+// SIG: every visible key's weight is sigmoid(score + bias[h]) by itself (no running maximum, no sum, no division at the end).
 // Sizes: key and value sizes are multiples of 16 up to 16 * DK16 / 16 * VD16 (template bounds; the real sizes are arguments).
 #include "mma_tiles.cuh"
 #include "seq_common.cuh"
@@ -15,12 +16,12 @@ namespace seqmix {
 
 constexpr int kQT = 64, kKT = 64, kPad = 8;     // queries / keys per tile; row padding (elements) against bank conflicts
 
-template <int DK16, int VD16>
+template <int DK16, int VD16, bool SIG>
 __global__ void __launch_bounds__(128)
 window_prompt_mma_kernel(const bf16* __restrict__ q, long q_sb, long q_st, const bf16* __restrict__ k, long k_sb, long k_st,
                          const bf16* __restrict__ v, long v_sb, long v_st, const bf16* __restrict__ gate, long g_sb, long g_st,
                          const int* __restrict__ lens, int S, int H, int G, int DK, int VD, int window, float scale, float softcap,
-                         bf16* __restrict__ out, long out_stride, float out_scale) {
+                         const float* __restrict__ score_bias, bf16* __restrict__ out, long out_stride, float out_scale) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int dk16 = DK / 16, vd16 = VD / 16, ldk = DK + kPad, ldv = VD + kPad;
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [kQT][ldk] queries, then key stage 1 (same size)
@@ -57,6 +58,7 @@ window_prompt_mma_kernel(const bf16* __restrict__ q, long q_sb, long q_st, const
     const float log2e = 1.4426950408889634f;
     const float scale2 = scale * log2e;                    // uncapped scores go straight to base 2
     const float cap_in = softcap > 0.f ? 2.f * log2e * scale / softcap : 0.f, cap_out = softcap * log2e;
+    const float sbias2 = SIG ? score_bias[h] * log2e : 0.f;
     const int jlo = max(0, q0 - window + 1), jhi = min(q0 + kQT - 1, len - 1);
     const bf16* kb = k + (long)b * k_sb + (long)hk * DK;
     const bf16* vb = v + (long)b * v_sb + (long)hk * VD;
@@ -123,10 +125,15 @@ window_prompt_mma_kernel(const bf16* __restrict__ q, long q_sb, long q_st, const
                 } else {
                     sc = sacc[n][e] * scale2;
                 }
-                sacc[n][e] = vis ? sc : -INFINITY;
-                mx[e >> 1] = fmaxf(mx[e >> 1], sacc[n][e]);
+                if (SIG) {                                 // sigmoid(x) = 1 / (1 + 2^(-x log2 e)); sc already holds x log2 e
+                    sacc[n][e] = vis ? __fdividef(1.f, 1.f + exp2f(fminf(-(sc + sbias2), 126.f))) : 0.f;
+                } else {
+                    sacc[n][e] = vis ? sc : -INFINITY;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], sacc[n][e]);
+                }
             }
         float corr[2], base[2];
+        if (!SIG) {
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
@@ -148,6 +155,7 @@ window_prompt_mma_kernel(const bf16* __restrict__ q, long q_sb, long q_st, const
         for (int r = 0; r < 2; ++r) lrow[r] = lrow[r] * corr[r] + ls[r];
 #pragma unroll
         for (int n = 0; n < 2 * VD16; ++n) { oacc[n][0] *= corr[0]; oacc[n][1] *= corr[0]; oacc[n][2] *= corr[1]; oacc[n][3] *= corr[1]; }
+        }
 #pragma unroll
         for (int kp = 0; kp < 4; ++kp) {
             unsigned pa[4];
@@ -172,6 +180,7 @@ window_prompt_mma_kernel(const bf16* __restrict__ q, long q_sb, long q_st, const
         lrow[r] += __shfl_xor_sync(0xffffffffu, lrow[r], 1);
         lrow[r] += __shfl_xor_sync(0xffffffffu, lrow[r], 2);
     }
+    if (SIG) lrow[0] = lrow[1] = 1.f;
     float inv0 = (i0 < len && lrow[0] > 0.f) ? out_scale / lrow[0] : 0.f, inv1 = (i1 < len && lrow[1] > 0.f) ? out_scale / lrow[1] : 0.f;
     if (gate) {
         if (i0 < len) inv0 *= sigmoidf_(__bfloat162float(gate[(long)b * g_sb + (long)i0 * g_st + h]));
@@ -197,20 +206,23 @@ bool window_prompt_mma_fits(const void* q, long q_sb, long q_st, const void* k, 
 
 void window_prompt_mma(const void* q, long q_sb, long q_st, const void* k, long k_sb, long k_st, const void* v, long v_sb, long v_st,
                        const void* gate, long g_sb, long g_st, const int* lens, int B, int S, int H, int G, int D, int V, int window,
-                       float scale, float softcap, void* out, long out_stride, float out_scale, cudaStream_t s) {
+                       float scale, float softcap, const float* score_bias, void* out, long out_stride, float out_scale, cudaStream_t s) {
     const size_t smem = (size_t)((kQT + kKT) * (D + kPad) + 2 * kKT * (V + kPad)) * sizeof(bf16);
     dim3 grid((S + kQT - 1) / kQT, H, B);
-#define SEQMIX_WPM(A, Bv)                                                                                                             \
+#define SEQMIX_WPM_S(A, Bv, SG)                                                                                                       \
     do {                                                                                                                              \
-        cudaFuncSetAttribute(window_prompt_mma_kernel<A, Bv>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);               \
-        window_prompt_mma_kernel<A, Bv><<<grid, 128, smem, s>>>((const bf16*)q, q_sb, q_st, (const bf16*)k, k_sb, k_st, (const bf16*)v,  \
-                                                               v_sb, v_st, (const bf16*)gate, g_sb, g_st, lens, S, H, G, D, V, window,  \
-                                                               scale, softcap, (bf16*)out, out_stride, out_scale);                    \
+        cudaFuncSetAttribute(window_prompt_mma_kernel<A, Bv, SG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);           \
+        window_prompt_mma_kernel<A, Bv, SG><<<grid, 128, smem, s>>>((const bf16*)q, q_sb, q_st, (const bf16*)k, k_sb, k_st,             \
+                                                                   (const bf16*)v, v_sb, v_st, (const bf16*)gate, g_sb, g_st, lens, S,  \
+                                                                   H, G, D, V, window, scale, softcap, score_bias, (bf16*)out,         \
+                                                                   out_stride, out_scale);                                            \
     } while (0)
+#define SEQMIX_WPM(A, Bv) do { if (score_bias) SEQMIX_WPM_S(A, Bv, true); else SEQMIX_WPM_S(A, Bv, false); } while (0)
     if (D <= 64 && V <= 64) SEQMIX_WPM(4, 4);
     else if (D <= 128 && V <= 128) SEQMIX_WPM(8, 8);
     else SEQMIX_WPM(16, 16);
 #undef SEQMIX_WPM
+#undef SEQMIX_WPM_S
 }
 
 }  // namespace seqmix

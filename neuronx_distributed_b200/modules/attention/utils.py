@@ -63,7 +63,8 @@ def deinterleave_index(heads: int, head_dim: int, off: int, dims: int) -> torch.
     other rows stay.  Reordering the rows of BOTH projections of a dot product (queries and keys) the same way leaves every score
     unchanged, so a checkpoint whose rotation pairs neighbours can be served by kernels that pair the two halves."""
     inner = torch.arange(head_dim)
-    inner[off:off + dims] = off + torch.cat([torch.arange(0, dims, 2), torch.arange(1, dims, 2)])
+    if dims > 0:
+        inner[off:off + dims] = off + torch.cat([torch.arange(0, dims, 2), torch.arange(1, dims, 2)])
     return (torch.arange(heads)[:, None] * head_dim + inner[None, :]).reshape(-1)
 
 
