@@ -54,6 +54,12 @@ def _load_pulenex(model_dir, dtype, device, max_seq_len, batch_size, **kw):
     return PulenexForInference.from_pretrained(model_dir, dtype=dtype, device=device, max_seq_len=max_seq_len, batch_size=batch_size, **kw)
 
 
+def _load_noresun(model_dir, dtype, device, max_seq_len, batch_size, **kw):
+    from .noresun import NoresunForInference
+
+    return NoresunForInference.from_pretrained(model_dir, dtype=dtype, device=device, max_seq_len=max_seq_len, batch_size=batch_size, **kw)
+
+
 def _load_hf_decoder(model_dir, dtype, device, max_seq_len, batch_size, **kw):
     """Llama / Mistral / Mixtral / DBRX checkpoints (model-parallel state must be initialised by the caller)."""
     from . import hf_compat
@@ -71,5 +77,6 @@ def _load_hf_decoder(model_dir, dtype, device, max_seq_len, batch_size, **kw):
 register_family("naguzen", _load_naguzen)
 register_family("pinirax", _load_pinirax)
 register_family("pulenex", _load_pulenex)
+register_family("noresun", _load_noresun)
 for _name in ("llama", "mistral", "qwen2", "mixtral", "dbrx"):
     register_family(_name, _load_hf_decoder)
