@@ -35,12 +35,13 @@ def parse():
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--mode", default="train", choices=["train", "decode", "pp", "naguzen", "pinirax", "pulenex"],
+    ap.add_argument("--mode", default="train", choices=["train", "decode", "pp", "naguzen", "pinirax", "pulenex", "noresun"],
                     help="train (default, the headline: Llama-2-7B training tokens/s) | decode (BASELINE config 5: Llama-2-13B "
                          "inference latency, batch 1, seq 2048) | pp (BASELINE config 4: GPT-NeoX-20B TP x PP=2 1F1B training) | "
                          "naguzen (serving throughput and per-kernel rooflines of the Naguzen design beside Llama at equal size) | "
                          "pinirax (the same for the Pinirax design beside Naguzen at equal size) | "
-                         "pulenex (the same for the Pulenex design beside Naguzen and Pinirax at equal size)")
+                         "pulenex (the same for the Pulenex design beside Naguzen and Pinirax at equal size) | "
+                         "noresun (the same for the Noresun design beside Pinirax and Naguzen at equal size)")
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--global-batch", type=int, default=4)
     ap.add_argument("--layers", type=int, default=32, help="32 = Llama-2-7B (anything else is a debug run)")
@@ -175,6 +176,10 @@ def main():
             import bench_pinirax
 
             return bench_pinirax.main(args)
+        if args.mode == "noresun":
+            import bench_noresun
+
+            return bench_noresun.main(args)
         if args.mode == "pulenex":
             import bench_pulenex
 
