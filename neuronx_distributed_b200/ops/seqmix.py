@@ -1,6 +1,8 @@
 """Sequence-mixer ops: short causal convolutions with carried history, scalar / vector RMS norms (optionally accumulated into a
-float residual stream), latent sliding-window attention over a ring cache, gated linear recurrences (per-key-channel decay; real-gated
-LRU), xIELU / erf-GELU and the small-batch pieces of a routed feed-forward.
+float residual stream, or closing a block whose norm follows a gated residual sum), token embeddings with sinusoids or a hashed
+pair table, latent / grouped-query / head-mixing sliding-window attention over ring caches (softmax or independent sigmoid weights),
+gated linear recurrences (per-key-channel decay; real-gated LRU; minGRU), matrix-state recurrences, xIELU / erf-GELU / squared relu
+and the small-batch pieces of a routed feed-forward.
 
 CUDA tensors run the hand-written kernels of ``csrc/seqmix`` (one small extension per kernel group, built in-tree on first use so
 that a fresh checkout compiles only the files of the mechanisms its model has); CPU tensors run the plain PyTorch statements below, which define the semantics.
